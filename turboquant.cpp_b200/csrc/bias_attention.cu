@@ -1,7 +1,8 @@
 // Attention with a learned distance bias, a window that keeps a sequence's first positions, and a sink in the
 // softmax's denominator, over a paged cache whose rows hold a key and a value of different sizes.
 //
-//   score(i, j) = q_i . k_j * scale + bias[min(i - j, far)][head]        (bias: a table per distance, or none)
+//   score(i, j) = cap(q_i . k_j * scale) + bias[min(i - j, far)][head]   (bias: a table per distance, or none;
+//                                                                          cap(s) = softcap * tanh(s / softcap), or s if softcap is 0)
 //   i sees j    iff j <= i and (window == 0 or i - j < window or j < keep_first)
 //   p_j         = exp(score_j) / (exp(sink[head]) + sum over the visible j of exp(score_j))   (sink: per head, or none)
 //   out_i       = sum_j p_j v_j
@@ -75,6 +76,78 @@ TQ_EXPORT int tq_bias_kv_write(const float* qkv, void* q_out, void* cache, int a
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// The same split with a rotation and a unit norm on the way: queries and keys are rotated by their token's position
+// (the first rot_dims elements of each head, pairs of neighbours or of halves, angle = position * freq[i] in fp32), then
+// each head is divided by its root mean square (unit_eps > 0: x / sqrt(mean(x^2) + unit_eps); 0: left as it is).
+// One block per token, a warp per head; values are copied.
+// ---------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128)
+bias_kv_write_rot_kernel(const float* __restrict__ qkv, int row_stride, TA* __restrict__ q_out, TA* __restrict__ cache,
+                         const float* __restrict__ freq, int rot_dims, int halves, float unit_eps,
+                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                         const int* __restrict__ page_table, int table_stride, int page_size,
+                         int nh, int nkv, int dk, int dv, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float s_head[4][BA_MAX_DIM];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv, dr = dk + dv;
+    const float* row = qkv + (size_t)t * row_stride;
+    const int pos = positions[t];
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+    const int page = TQ_CHECKED(table[TQ_CHECKED(pos / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+    const int slot = pos % page_size;
+    for (int head = warp; head < nh + nkv; head += 4) {
+        const float* src = row + (size_t)head * dk;            // keys follow the queries in the row
+        float* sh = s_head[warp];
+        __syncwarp();
+        for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+        __syncwarp();
+        float v[BA_EPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < BA_EPL; ++j) {
+            const int e = lane + 32 * j;
+            v[j] = e < dk ? tq_rotated(sh, e, rot_dims, halves, freq, pos) : 0.f;
+            ss += v[j] * v[j];
+        }
+        float rs = 1.f;
+        if (unit_eps > 0.f) rs = 1.0f / sqrtf(tq_warp_sum(ss) / (float)dk + unit_eps);
+        TA* dst = head < nh ? q_out + ((size_t)t * nh + head) * dk
+                            : (cache ? cache + (((size_t)page * nkv + (head - nh)) * page_size + slot) * dr : nullptr);
+        if (dst == nullptr) continue;
+#pragma unroll
+        for (int j = 0; j < BA_EPL; ++j) {
+            const int e = lane + 32 * j;
+            if (e < dk) dst[e] = tq_from_float<TA>(v[j] * rs);
+        }
+    }
+    if (cache == nullptr) return;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int g = i / dv, e = i % dv;
+        cache[(((size_t)page * nkv + g) * page_size + slot) * dr + dk + e] = tq_from_float<TA>(row[nq + nk + i]);
+    }
+}
+
+// qkv: fp32 rows of row_stride floats that begin with [q | k | v]; freq: fp32 [rot_dims / 2] (null with rot_dims 0).
+TQ_EXPORT int tq_bias_kv_write_rot(const float* qkv, int row_stride, void* q_out, void* cache, int act_dtype,
+                                   const float* freq, int rot_dims, int halves, float unit_eps, const int* positions,
+                                   const int* seq_of_token, const int* page_table, int table_stride, int page_size,
+                                   int T_, int nh, int nkv, int dk, int dv, int n_seqs, int n_pages, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(nh >= 1 && nkv >= 1 && dk >= 1 && dv >= 1 && dk <= BA_MAX_DIM, "bias_kv_write_rot: bad sizes %d %d %d %d", nh, nkv, dk, dv);
+    TQ_REQUIRE(row_stride >= nh * dk + nkv * (dk + dv), "bias_kv_write_rot: rows of %d floats do not hold the heads", row_stride);
+    TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
+               "bias_kv_write_rot: %d rotated elements of a head of %d", rot_dims, dk);
+    TQ_DISPATCH(act_dtype, TA,
+        (tq_launch(T_, 128, 0, stream)(bias_kv_write_rot_kernel<TA>, qkv, row_stride, (TA*)q_out, (TA*)cache, freq, rot_dims,
+            halves, unit_eps, positions, seq_of_token, page_table, table_stride, page_size, nh, nkv, dk, dv, n_seqs, n_pages)));
+    TQ_CHECK_LAUNCH("bias_kv_write_rot");
+    return 0;
+}
+
 // The visible positions of a query at `pos`, in order: [0, n_first) and [start, pos].
 struct BaSpan {
     int n_first, start, count;
@@ -99,7 +172,7 @@ __global__ void __launch_bounds__(BA_WARPS * 32)
 bias_attention_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const float* __restrict__ bias, int far,
                       const float* __restrict__ sink, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
-                      int page_size, int window, int keep_first, float scale, TA* __restrict__ out,
+                      int page_size, int window, int keep_first, float scale, float softcap, TA* __restrict__ out,
                       float* __restrict__ partial, int n_splits, int nh, int nkv, int dk, int dv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -135,6 +208,7 @@ bias_attention_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, co
             if (e < dk) s += qv[j] * tq_to_float(kp[e]);
         }
         s = tq_warp_sum(s);
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         if (bias) s += bias[(size_t)min(pos - p, far) * nh + h];
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);          // exp(-inf) = 0 on the first key
@@ -210,7 +284,7 @@ __global__ void bias_attention_merge_kernel(const float* __restrict__ partial, i
 TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype, const float* bias, int far,
                                 const float* sink, const int* positions, const int* seq_of_token,
                                 const int* page_table, int table_stride, int page_size, int window, int keep_first,
-                                float scale, void* out, float* partial, int n_splits, int T_, int nh, int nkv, int dk,
+                                float scale, float softcap, void* out, float* partial, int n_splits, int T_, int nh, int nkv, int dk,
                                 int dv, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(dk >= 1 && dk <= BA_MAX_DIM && dv >= 1 && dv <= BA_MAX_DIM, "bias_attention: key size %d or value size %d exceeds %d", dk, dv, BA_MAX_DIM);
@@ -221,7 +295,7 @@ TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype,
     dim3 grid(T_, nh, n_splits);
     TQ_DISPATCH(act_dtype, TA,
         (tq_launch(grid, BA_WARPS * 32, 0, stream)(bias_attention_kernel<TA>, (const TA*)q, (const TA*)cache, bias, far, sink,
-            positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, (TA*)out, partial,
+            positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, (TA*)out, partial,
             n_splits, nh, nkv, dk, dv, n_seqs, n_pages)));
     TQ_CHECK_LAUNCH("bias_attention");
     if (n_splits > 1) {
@@ -261,7 +335,7 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ page_table, int table_stride, int page_size, int window,
-                            int keep_first, float scale, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int keep_first, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                             int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -372,6 +446,7 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             for (int j = 0; j < LOADS; ++j) {
                 const int n = base + j * KPI + part;
                 if (n < n1) {
+                    if (softcap > 0.f) s[j][h] = softcap * tanhf(s[j][h] / softcap);
                     if (bias_t) s[j][h] += __ldg(bias_t + (size_t)(h0 + h) * (far + 1) + min(pos - span.at(n), far));
                 } else s[j][h] = -INFINITY;
                 mx = fmaxf(mx, s[j][h]);
@@ -461,7 +536,7 @@ TQ_EXPORT int tq_bias_attention_group_heads(int dk, int dv, int per_kv) { return
 
 TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                                       const int* positions, const int* seq_of_token, const int* page_table,
-                                      int table_stride, int page_size, int window, int keep_first, float scale, void* out,
+                                      int table_stride, int page_size, int window, int keep_first, float scale, float softcap, void* out,
                                       float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
                                       int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
@@ -487,7 +562,7 @@ TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const fl
         }                                                                                                             \
         tq_launch(grid, BA_WARPS * 32, ring_bytes, stream)(bias_attention_group_kernel<DK_, DV_, GC_>, (const __nv_bfloat16*)q,  \
             (const __nv_bfloat16*)cache, bias_t, far, sink, positions, seq_of_token, page_table, table_stride, page_size, \
-            window, keep_first, scale, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
+            window, keep_first, scale, softcap, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
         done = true;                                                                                                  \
     }
 #define BG_SHAPE(DK_, DV_) BG_CASE(DK_, DV_, 1) BG_CASE(DK_, DV_, 2) BG_CASE(DK_, DV_, 4)
@@ -543,7 +618,7 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                            const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                            const int* __restrict__ page_table, int table_stride, int window, int keep_first,
-                           float scale, __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_pages) {
+                           float scale, float softcap, __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     constexpr int DR = DK + DV, LD = DR + 8;                 // a shared-memory row: key, value, 16 bytes of padding
@@ -652,6 +727,7 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                     const int d = i - p;
                     const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
                     float v = s[n][c] * scale;
+                    if (softcap > 0.f) v = softcap * tanhf(v / softcap);
                     if (biased) v += sb[min(max(d - d_min, 0), BR_Q + BR_K - 2)];
                     v = see ? v : -INFINITY;
                     s[n][c] = v;
@@ -728,7 +804,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ page_table, int table_stride, int page_size, int window,
-                            int keep_first, float scale, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int keep_first, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                             int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -814,6 +890,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                 const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
                 const float* bh = (c & 2) ? b_hi : b_lo;
                 float v = s[n][c] * scale;
+                if (softcap > 0.f) v = softcap * tanhf(v / softcap);
                 if (bh && see) v += __ldg(bh + min(d, far));
                 v = see ? v : -INFINITY;
                 s[n][c] = v;
@@ -900,7 +977,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 template <int DK, int DV>
 int launch_bias_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink, const int* positions,
                       const int* seq_of_token, const int* page_table, int table_stride, int page_size, int window,
-                      int keep_first, float scale, void* out, float* partial, int n_splits, int T_, int nh, int nkv,
+                      int keep_first, float scale, float softcap, void* out, float* partial, int n_splits, int T_, int nh, int nkv,
                       int n_seqs, int n_pages, cudaStream_t stream) {
     auto kern = bias_attention_heads_kernel<DK, DV>;
     const int ring = BA_WARPS * 2 * BH_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
@@ -915,14 +992,14 @@ int launch_bias_heads(const void* q, const void* cache, const float* bias_t, int
     const int chunks = (nh / nkv + 15) / 16;
     dim3 grid(T_, nkv * chunks, n_splits);
     tq_launch(grid, BA_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far, sink,
-        positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, (__nv_bfloat16*)out, partial,
+        positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, (__nv_bfloat16*)out, partial,
         n_splits, nh, nkv, n_seqs, n_pages);
     return 0;
 }
 
 TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                                       const int* positions, const int* seq_of_token, const int* page_table,
-                                      int table_stride, int page_size, int window, int keep_first, float scale, void* out,
+                                      int table_stride, int page_size, int window, int keep_first, float scale, float softcap, void* out,
                                       float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
                                       int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
@@ -934,7 +1011,7 @@ TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const fl
     TQ_REQUIRE(n_splits == 1 || partial != nullptr, "bias_attention_heads: %d ranges need scratch for their states", n_splits);
     int rc = -2;
 #define BH_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_heads<DK_, DV_>(q, cache, bias_t, far, sink, positions, \
-        seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, out, partial, n_splits, T_, nh, nkv,  \
+        seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, out, partial, n_splits, T_, nh, nkv,  \
         n_seqs, n_pages, stream);
     BH_CASE(32, 32) BH_CASE(32, 64) BH_CASE(32, 128) BH_CASE(64, 32) BH_CASE(64, 64) BH_CASE(64, 128)
     BH_CASE(128, 32) BH_CASE(128, 64) BH_CASE(128, 128)
@@ -952,7 +1029,7 @@ TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const fl
 template <int DK, int DV>
 int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                      const int* cu_seqlens, const int* seq_start, const int* page_table, int table_stride, int window,
-                     int keep_first, float scale, void* out, int n_seqs, int max_run, int nh, int nkv, int n_pages,
+                     int keep_first, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv, int n_pages,
                      cudaStream_t stream) {
     auto kern = bias_attention_runs_kernel<DK, DV>;
     const int smem = 2 * BR_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
@@ -964,7 +1041,7 @@ int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int 
     }
     dim3 grid(nh, n_seqs, (max_run + BR_Q - 1) / BR_Q);
     tq_launch(grid, BR_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far,
-        sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, scale, (__nv_bfloat16*)out, nh, nkv, n_pages);
+        sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, scale, softcap, (__nv_bfloat16*)out, nh, nkv, n_pages);
     return 0;
 }
 
@@ -972,7 +1049,7 @@ int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int 
 TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_dtype, const float* bias_t, int far,
                                      const float* sink, const int* cu_seqlens, const int* seq_start,
                                      const int* page_table, int table_stride, int page_size, int window,
-                                     int keep_first, float scale, void* out, int n_seqs, int max_run, int nh, int nkv,
+                                     int keep_first, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv,
                                      int dk, int dv, int n_pages, cudaStream_t stream) {
     if (n_seqs == 0 || max_run == 0) return 0;
     TQ_REQUIRE(act_dtype == TQ_BF16, "bias_attention_runs: bfloat16 only");
@@ -982,7 +1059,7 @@ TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_d
     TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_runs: negative window, kept positions or distance");
     int rc = -2;
 #define BR_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_runs<DK_, DV_>(q, cache, bias_t, far, sink, cu_seqlens, \
-        seq_start, page_table, table_stride, window, keep_first, scale, out, n_seqs, max_run, nh, nkv, n_pages, stream);
+        seq_start, page_table, table_stride, window, keep_first, scale, softcap, out, n_seqs, max_run, nh, nkv, n_pages, stream);
     BR_CASE(32, 32) BR_CASE(32, 64) BR_CASE(32, 128) BR_CASE(64, 32) BR_CASE(64, 64) BR_CASE(64, 128)
     BR_CASE(128, 32) BR_CASE(128, 64) BR_CASE(128, 128)
 #undef BR_CASE

@@ -96,14 +96,36 @@ template <> __device__ __forceinline__ __nv_bfloat16 tq_from_float<__nv_bfloat16
 }
 
 // Gated activation of the feed-forwards: g = min(gate, limit), u = clamp(up, -limit, limit),
-// g * sigmoid(slope * g) * (u + offset).  limit = +inf, slope = 1, offset = 0 is silu(gate) * up, bit for bit.
-struct TqGlu { float limit, slope, offset; };
+// act(g) * (u + offset) with act(g) = g * sigmoid(slope * g) (kind 0), or the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) (kind 1).  limit = +inf, slope = 1, offset = 0, kind 0 is
+// silu(gate) * up, bit for bit.
+#define TQ_GLU_SIGMOID 0
+#define TQ_GLU_GELU_TANH 1
+struct TqGlu { float limit, slope, offset; int kind; };
+__device__ __forceinline__ float tq_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 __device__ __forceinline__ float tq_glu(float gate, float up, TqGlu p) {
     const float g = fminf(gate, p.limit), u = fminf(fmaxf(up, -p.limit), p.limit);
+    if (p.kind == TQ_GLU_GELU_TANH) return tq_gelu_tanh(g) * (u + p.offset);
     return g / (1.0f + expf(-p.slope * g)) * (u + p.offset);
 }
-inline TqGlu tq_glu_params(float limit, float slope, float offset) {
-    TqGlu p; p.limit = limit > 0.f ? limit : INFINITY; p.slope = slope; p.offset = offset; return p;
+inline TqGlu tq_glu_params(float limit, float slope, float offset, int kind = TQ_GLU_SIGMOID) {
+    TqGlu p; p.limit = limit > 0.f ? limit : INFINITY; p.slope = slope; p.offset = offset; p.kind = kind; return p;
+}
+
+// Element e of a head after the rotation of its first `dims` elements by the angles pos * freq[i] (float32):
+// pairs (2i, 2i+1) (halves == 0) or (i, i + dims/2) (halves != 0); the pair (u, v) becomes
+// (u cos - v sin, v cos + u sin).  Elements from `dims` on pass unchanged.  `head` holds the unrotated values.
+__device__ __forceinline__ float tq_rotated(const float* head, int e, int dims, int halves, const float* __restrict__ freq, int pos) {
+    if (e >= dims) return head[e];
+    int i, partner;
+    bool first;
+    if (halves) { const int half = dims >> 1; first = e < half; i = first ? e : e - half; partner = first ? e + half : e - half; }
+    else { i = e >> 1; first = !(e & 1); partner = e ^ 1; }
+    float sn, cs;
+    sincosf((float)pos * freq[i], &sn, &cs);
+    return first ? head[e] * cs - head[partner] * sn : head[e] * cs + head[partner] * sn;
 }
 
 __device__ __forceinline__ float tq_warp_sum(float v) {

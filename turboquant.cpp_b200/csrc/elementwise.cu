@@ -274,10 +274,11 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, i
 
 // limit <= 0: no caps.  (limit, slope, offset) = (0, 1, 0): silu(gate) * up.
 TQ_EXPORT int tq_glu_mul(const void* gu, int in_dtype, void* h, int out_dtype, int T_, int I, float limit, float slope,
-                         float offset, cudaStream_t stream) {
+                         float offset, int kind, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ > 0 && I > 0, "glu_mul: bad sizes T=%d I=%d", T_, I);
-    const TqGlu act = tq_glu_params(limit, slope, offset);
+    TQ_REQUIRE(kind == TQ_GLU_SIGMOID || kind == TQ_GLU_GELU_TANH, "glu_mul: unknown activation kind %d", kind);
+    const TqGlu act = tq_glu_params(limit, slope, offset, kind);
     TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(T_, 256, 0, stream)(silu_mul_kernel<TI, TO>, (const TI*)gu, (TO*)h, I, act))));
     TQ_CHECK_LAUNCH("glu_mul");
@@ -563,5 +564,90 @@ TQ_EXPORT int tq_rotate_pairs(void* x, int dtype, const float* freq, const int* 
         tq_launch(T_, 128, 0, stream)(rotate_pairs_kernel<TX>, (TX*)x, freq, positions, heads, head_stride, token_stride,
                                       offset, n_pairs, mag));
     TQ_CHECK_LAUNCH("rotate_pairs");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// The mean of two branches, each under an RMS norm of its own:
+//   out[r] = (a[r] / sqrt(mean(a[r]^2) + eps) * wa + b[r] / sqrt(mean(b[r]^2) + eps) * wb) / 2, in fp32.
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void mean_of_norms_kernel(const float* __restrict__ a, const TW* __restrict__ wa, const float* __restrict__ b,
+                                     const TW* __restrict__ wb, float* __restrict__ out, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const float* ar = a + r * H;
+    const float* br = b + r * H;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float u = ar[i], v = br[i];
+        sa += u * u;
+        sb += v * v;
+    }
+    sa = tq_block_sum(sa, scratch);
+    sb = tq_block_sum(sb, scratch);
+    const float ra = 1.0f / sqrtf(sa / (float)H + eps), rb = 1.0f / sqrtf(sb / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[r * H + i] = 0.5f * (ar[i] * ra * tq_to_float(wa[i]) + br[i] * rb * tq_to_float(wb[i]));
+}
+
+TQ_EXPORT int tq_mean_of_norms(const float* a, const void* wa, const float* b, const void* wb, int w_dtype, float* out,
+                               int R, int H, float eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(R > 0 && H > 0, "mean_of_norms: bad sizes R=%d H=%d", R, H);
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    TQ_DISPATCH(w_dtype, TW,
+        (tq_launch(R, threads, 0, stream)(mean_of_norms_kernel<TW>, a, (const TW*)wa, b, (const TW*)wb, out, H, eps)));
+    TQ_CHECK_LAUNCH("mean_of_norms");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// A gated activation against rows of a table: out[t, j] = glu(z[t, j], table[tokens[t]][col0 + j]) for j < D
+// (z fp32 [T, D]; the table's rows have `stride` elements).
+// ---------------------------------------------------------------------------------------
+template <typename TT, typename TO>
+__global__ void glu_table_rows_kernel(const float* __restrict__ z, const int* __restrict__ tokens, const TT* __restrict__ table,
+                                      int stride, int col0, TO* __restrict__ out, int D, int vocab, TqGlu act) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const size_t t = blockIdx.x;
+    const TT* row = table + (size_t)TQ_CHECKED(tokens[t], vocab, TQ_IDX_TOKEN) * stride + col0;
+    for (int j = threadIdx.x; j < D; j += blockDim.x)
+        out[t * D + j] = tq_from_float<TO>(tq_glu(z[t * D + j], tq_to_float(row[j]), act));
+}
+
+TQ_EXPORT int tq_glu_table_rows(const float* z, const int* tokens, const void* table, int table_dtype, int stride, int col0,
+                                void* out, int out_dtype, int T_, int D, int vocab, float limit, float slope, float offset,
+                                int kind, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(D > 0 && col0 >= 0 && col0 + D <= stride, "glu_table_rows: columns %d..%d of rows of %d", col0, col0 + D, stride);
+    TQ_REQUIRE(kind == TQ_GLU_SIGMOID || kind == TQ_GLU_GELU_TANH, "glu_table_rows: unknown activation kind %d", kind);
+    const TqGlu act = tq_glu_params(limit, slope, offset, kind);
+    const int threads = D >= 256 ? 256 : (D >= 64 ? 64 : 32);
+    TQ_DISPATCH(table_dtype, TT, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch(T_, threads, 0, stream)(glu_table_rows_kernel<TT, TO>, z, tokens, (const TT*)table, stride, col0, (TO*)out, D,
+                                           vocab, act))));
+    TQ_CHECK_LAUNCH("glu_table_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// x[t, j] = x[t, j] * scale + bias[j] for j < N, rows of `stride` floats (bias may be null).
+// ---------------------------------------------------------------------------------------
+__global__ void scale_bias_cols_kernel(float* __restrict__ x, const float* __restrict__ bias, float scale, int N, int stride) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    float* row = x + (size_t)blockIdx.x * stride;
+    for (int j = threadIdx.x; j < N; j += blockDim.x) row[j] = bias ? row[j] * scale + bias[j] : row[j] * scale;
+}
+
+TQ_EXPORT int tq_scale_bias_cols(float* x, const float* bias, float scale, int T_, int N, int stride, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(N > 0 && N <= stride, "scale_bias_cols: %d columns of rows of %d", N, stride);
+    tq_launch(T_, N >= 1024 ? 256 : 128, 0, stream)(scale_bias_cols_kernel, x, bias, scale, N, stride);
+    TQ_CHECK_LAUNCH("scale_bias_cols");
     return 0;
 }

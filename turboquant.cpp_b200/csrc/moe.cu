@@ -81,7 +81,8 @@ template <> struct RowVec<float> {
 // Kernel 1: logits[t, e] = x[t] . w[e] for a chunk of rows (grid: tokens x row chunks).
 template <typename TA, typename TW, bool STAGED>
 __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
-                                     float* __restrict__ logits, int H, int E, int rows_per_cta, int vec_ok) {
+                                     float* __restrict__ logits, int H, int E, int rows_per_cta, int vec_ok,
+                                     const float* __restrict__ logit_bias) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     extern __shared__ float s_x[];
@@ -107,7 +108,7 @@ __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restr
         }
         for (int i = Hv + lane; i < H; i += 32) s = fmaf(STAGED ? s_x[i] : tq_to_float(xr[i]), tq_to_float(w[i]), s);
         s = tq_warp_sum(s);
-        if (lane == 0) logits[(size_t)t * (E + 1) + e] = s;
+        if (lane == 0) logits[(size_t)t * (E + 1) + e] = (logit_bias && e < E) ? s + logit_bias[e] : s;
     }
 }
 
@@ -231,7 +232,7 @@ __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict
 // logits: T * (E + 1) floats of scratch.
 TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
                              float* logits, int* ids, float* wts, float* shared_scale, int T_, int H, int E, int k,
-                             int renorm, cudaStream_t stream) {
+                             int renorm, const float* logit_bias, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
     TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
@@ -253,7 +254,7 @@ TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const
 #define ROUTER_LAUNCH(ST)                                                                              \
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
         (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                             \
-            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok, logit_bias))))
     if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
 #undef ROUTER_LAUNCH
     TQ_CHECK_LAUNCH("router_logits");
@@ -388,7 +389,7 @@ TQ_EXPORT int tq_router_select_corrected(const float* logits, const float* corre
 
 // The logits alone (what tq_router_topk computes before it chooses): logits [T, E + 1], column E the shared gate's.
 TQ_EXPORT int tq_router_logits(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
-                               float* logits, int T_, int H, int E, cudaStream_t stream) {
+                               float* logits, int T_, int H, int E, const float* logit_bias, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
     const bool staged = H <= ROUTER_MAX_STAGED_H;
@@ -406,7 +407,7 @@ TQ_EXPORT int tq_router_logits(const void* x, int act_dtype, const void* wr, con
 #define ROUTER_LAUNCH(ST)                                                                              \
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
         (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                             \
-            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok, logit_bias))))
     if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
 #undef ROUTER_LAUNCH
     TQ_CHECK_LAUNCH("router_logits");
@@ -670,7 +671,8 @@ router_cluster_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const
                       int T_, int H, int E, int k, int renorm, int vec_dot, int tile_rows,
                       int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
                       int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                      int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x) {
+                      int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x,
+                      const float* __restrict__ logit_bias) {
     const unsigned rank = small_cluster_rank();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     // a block's shared memory may be written by its peers only once it runs: every block says so here and
@@ -731,8 +733,9 @@ router_cluster_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const
         s = tq_warp_sum(s);
         s2 = tq_warp_sum(s2);
         if (lane == 0) {
-            small_st_peer(&s_logit[e], (unsigned)t0, s);
-            if (t1 != t0) small_st_peer(&s_logit[e], (unsigned)t1, s2);
+            const float lb = (logit_bias && e < E) ? logit_bias[e] : 0.f;       // a bias on the experts' logits
+            small_st_peer(&s_logit[e], (unsigned)t0, logit_bias ? s + lb : s);
+            if (t1 != t0) small_st_peer(&s_logit[e], (unsigned)t1, logit_bias ? s2 + lb : s2);
         }
     }
     small_cluster_sync();                                     // every token's logits are in its block
@@ -792,7 +795,8 @@ router_tiny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_scale, int H, int E, int k,
                    int renorm, int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
                    int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                   int* __restrict__ tile_count, int* __restrict__ n_tiles, __nv_bfloat16* __restrict__ x_rows) {
+                   int* __restrict__ tile_count, int* __restrict__ n_tiles, __nv_bfloat16* __restrict__ x_rows,
+                   const float* __restrict__ logit_bias) {
     extern __shared__ __align__(16) unsigned char s_tiny[];
     __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(s_tiny);                     // [T][H]
     float* s_logit = reinterpret_cast<float*>(s_tiny + (size_t)T * H * 2);             // [T][E + 1]
@@ -847,8 +851,8 @@ router_tiny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         for (int t = 0; t < T; ++t) {
             const float va = tq_warp_sum(sa[t]), vb = tq_warp_sum(sb[t]);
             if (lane == 0) {
-                s_logit[t * (E + 1) + r0] = va;
-                if (r1 < rows) s_logit[t * (E + 1) + r1] = vb;
+                s_logit[t * (E + 1) + r0] = (logit_bias && r0 < E) ? va + logit_bias[r0] : va;
+                if (r1 < rows) s_logit[t * (E + 1) + r1] = (logit_bias && r1 < E) ? vb + logit_bias[r1] : vb;
             }
         }
     }
@@ -909,7 +913,7 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
                     int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                     int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x,
                     int* __restrict__ counter, const float* __restrict__ correction, int corrected, float floor_,
-                    int n_groups, int keep_groups) {
+                    int n_groups, int keep_groups, const float* __restrict__ logit_bias) {
     tq_grid_wait();
     tq_grid_launch_dependents();
     extern __shared__ float s_dyn[];
@@ -946,7 +950,10 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
         }
         s = tq_warp_sum(s);
         s2 = tq_warp_sum(s2);
-        if (lane == 0) { s_logit[e] = s; s_logit[e2] = s2; }      // e2 == e: the same value twice
+        if (lane == 0) {                                           // e2 == e: the same value twice
+            s_logit[e] = (logit_bias && e < E) ? s + logit_bias[e] : s;
+            s_logit[e2] = (logit_bias && e2 < E) ? s2 + logit_bias[e2] : s2;
+        }
     }
     __syncthreads();
     // ---- selection: warp 0 (the same choices and weights as router_select_kernel) ----
@@ -1046,7 +1053,7 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
                               int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0, int* tile_count,
                               int* n_tiles, void* x_rows, int* counter, int T_, int H, int E, int k, int renorm,
                               const float* correction, int corrected, float floor_, int n_groups, int keep_groups,
-                              cudaStream_t stream) {
+                              const float* logit_bias, cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (corrected) {            // corrected scores, groups, a floor under the weights' sum: the counter form knows them
         TQ_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
@@ -1077,7 +1084,7 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
             H % 8 == 0 && vec_w && vec_x && E <= 32 * SELECT_REGS && smem_tiny <= 40 * 1024) {
 #define TINY_CASE(TT) case TT: tq_launch(1, TINY_THREADS, smem_tiny, stream)(router_tiny_kernel<TT>, (const __nv_bfloat16*)x, \
             (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, ids, wts, shared_scale, H, E, k, renorm, counts, sorted_pair,  \
-            row_of_pair, expert_offset, tile_expert, tile_row0, tile_count, n_tiles, (__nv_bfloat16*)x_rows); break;
+            row_of_pair, expert_offset, tile_expert, tile_row0, tile_count, n_tiles, (__nv_bfloat16*)x_rows, logit_bias); break;
             switch (T_) { TINY_CASE(1) TINY_CASE(2) TINY_CASE(3) TINY_CASE(4) }
 #undef TINY_CASE
             TQ_CHECK_LAUNCH("router_tiny");
@@ -1096,14 +1103,14 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
         TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
             (cfg = launch_router_cluster<TA, TW>(smem_cluster, stream, (const TA*)x, (const TW*)wr, (const TW*)wsg,
                 ids, wts, shared_scale, T_, H, E, k, renorm, vec_dot, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
-                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x))));
+                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, logit_bias))));
         TQ_REQUIRE(cfg == cudaSuccess, "router_small: %zu bytes of shared memory refused: %s", smem_cluster, cudaGetErrorString(cfg));
     } else {
         TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
             (tq_launch(T_, SMALL_THREADS, smem, stream)(router_small_kernel<TA, TW>, (const TA*)x, (const TW*)wr, (const TW*)wsg,
                 ids, wts, shared_scale, T_, H, E, k, renorm, vec_w, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
                 tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter, correction, corrected, floor_,
-                n_groups, keep_groups))));
+                n_groups, keep_groups, logit_bias))));
     }
     TQ_CHECK_LAUNCH("router_small");
     return 0;

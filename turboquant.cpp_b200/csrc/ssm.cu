@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(32 * SSM_COLS / SSM_CPW)
 ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, float* __restrict__ y, int heads, int vdim, int N,
-                int groups, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+                int groups, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                const float* __restrict__ fixed_decay) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     constexpr int SSM_WARPS = SSM_COLS / SSM_CPW, SSM_GROUP = 32 / SSM_CPW;
@@ -148,7 +149,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
     const int g = h / (heads / groups);
     const int inner = heads * vdim;
     const int first = cu_seqlens[s], n = cu_seqlens[s + 1] - first;
-    const float A = -expf(tq_to_float(a_log[h])), bias = tq_to_float(dt_bias[h]), D = tq_to_float(d_skip[h]);
+    // fixed_decay: the recurrence S <- decay[h] S + B x^T, y = S^T C with a constant decay per head, a step size of
+    // one and no skip term (the per-head constants and the raw step sizes are not read)
+    const bool fixed = fixed_decay != nullptr;
+    const float A = fixed ? 0.f : -expf(tq_to_float(a_log[h])), bias = fixed ? 0.f : tq_to_float(dt_bias[h]);
+    const float D = fixed ? 0.f : tq_to_float(d_skip[h]), decay_h = fixed ? fixed_decay[h] : 0.f;
     float* Sg = state + (size_t)slots[s] * slot_stride + ((size_t)h * N) * vdim;
     float S[RPL][SSM_CPW];
 #pragma unroll
@@ -179,7 +184,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
             const int k = tid + i * NT, tt = k / SSM_COLS, vv = v0 + k % SSM_COLS;
             px[i] = (tt < tc && vv < vdim) ? xbc[(size_t)(first + t0 + tt) * C + (size_t)h * vdim + vv] : 0.f;
         }
-        if (tid < tc) praw = proj[(size_t)(first + t0 + tid) * P + dt_off + h];
+        if (tid < tc && !fixed) praw = proj[(size_t)(first + t0 + tid) * P + dt_off + h];
     };
     if (n > 0) fetch(0);
     for (int t0 = 0; t0 < n; t0 += TC) {
@@ -193,9 +198,9 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
         for (int i = 0; i < XPT; ++i) xs[tid + i * NT] = px[i];
         if (tid < tc) {
             const float raw = praw + bias;
-            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            const float dt = fixed ? 1.0f : (raw > 20.f ? raw : log1pf(expf(raw)));
             dts[tid] = dt;
-            dec[tid] = expf(A * dt);
+            dec[tid] = fixed ? decay_h : expf(A * dt);
         }
         __syncthreads();
         if (t0 + TC < n) fetch(t0 + TC);
@@ -264,7 +269,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
     TQ_DISPATCH(w_dtype, TW,                                                                                      \
         (tq_launch(grid, 32 * SSM_COLS / CPW_, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_, CPW_>, xbc, C, proj, P, dt_off, \
             (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, \
-            cu_seqlens, slots)))
+            cu_seqlens, slots, fixed_decay)))
 
 // TQ_SSM_CPW=2: sixteen warps of two columns instead of eight of four (measured slower at every size tried)
 static int ssm_cpw() {
@@ -275,12 +280,13 @@ static int ssm_cpw() {
 TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
                           const void* a_log, const void* d_skip, int w_dtype, float* state, long long slot_stride,
                           float* y, int n_seqs, int heads, int vdim, int N, int groups, const int* cu_seqlens,
-                          const int* slots, cudaStream_t stream) {
+                          const int* slots, const float* fixed_decay, cudaStream_t stream) {
     if (n_seqs == 0) return 0;
+    if (fixed_decay != nullptr) w_dtype = TQ_F32;        // the per-head tensors are not read
     TQ_REQUIRE(heads >= 1 && vdim >= 1 && groups >= 1 && heads % groups == 0, "ssm_scan: %d heads in %d groups", heads, groups);
     TQ_REQUIRE(N >= 1 && N <= SSM_MAX_STATE, "ssm_scan: state size %d (1..%d)", N, SSM_MAX_STATE);
     TQ_REQUIRE(C == heads * vdim + 2 * groups * N, "ssm_scan: %d channels for %d heads x %d and %d groups x %d", C, heads, vdim, groups, N);
-    TQ_REQUIRE(dt_off >= 0 && dt_off + heads <= P, "ssm_scan: the step sizes lie outside the projection");
+    TQ_REQUIRE(fixed_decay != nullptr || (dt_off >= 0 && dt_off + heads <= P), "ssm_scan: the step sizes lie outside the projection");
     const int RPL = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 128 ? 4 : 8));
     const int NP = 32 * RPL;
     const int TC = NP <= 64 ? 32 : 16;
@@ -304,12 +310,14 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
 
 // ---------------------------------------------------------------------------------------
 // out[t, g-th part] = rms(y[t, part] * silu(z[t, part])) * w[part]: the gate first, then the norm of each of the
-// `norm_groups` equal parts by its own root mean square.  z is the first `inner` elements of the projection's row.
+// `norm_groups` equal parts by its own root mean square.  z is `inner` elements of the projection's row from z_off.
+// gate_after: the norm first, then the gate: rms(y[t, part]) * w[part] * silu(z[t, part]).  w may be null (no weight).
 // ---------------------------------------------------------------------------------------
 #define GGN_KEEP 8
 template <typename TW, typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
-                                        const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, float eps) {
+                                        const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, float eps,
+                                        int gate_after) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
@@ -317,7 +325,8 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     const int base = blockIdx.y * gs;
     const float* yr = y + t * inner + base;
     const float* zr = proj + t * P + z_off + base;
-    // a thread's gated values stay in registers between the sum of squares and the output (up to GGN_KEEP of them;
+    auto silu = [](float z) { return z / (1.0f + expf(-z)); };
+    // a thread's (gated) values stay in registers between the sum of squares and the output (up to GGN_KEEP of them;
     // longer parts compute the rest again)
     float keep[GGN_KEEP];
     float ss = 0.f;
@@ -325,14 +334,11 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     for (int k = 0; k < GGN_KEEP; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
         keep[k] = 0.f;
-        if (i < gs) {
-            const float z = zr[i];
-            keep[k] = yr[i] * (z / (1.0f + expf(-z)));
-        }
+        if (i < gs) keep[k] = gate_after ? yr[i] : yr[i] * silu(zr[i]);
         ss += keep[k] * keep[k];
     }
     for (int i = threadIdx.x + GGN_KEEP * blockDim.x; i < gs; i += blockDim.x) {
-        const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
+        const float v = gate_after ? yr[i] : yr[i] * silu(zr[i]);
         ss += v * v;
     }
     ss = tq_block_sum(ss, scratch);
@@ -340,16 +346,21 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
 #pragma unroll
     for (int k = 0; k < GGN_KEEP; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
-        if (i < gs) out[t * inner + base + i] = tq_from_float<TO>(keep[k] * rs * tq_to_float(w[base + i]));
+        if (i < gs) {
+            float v = keep[k] * rs * (w ? tq_to_float(w[base + i]) : 1.0f);
+            if (gate_after) v *= silu(zr[i]);
+            out[t * inner + base + i] = tq_from_float<TO>(v);
+        }
     }
     for (int i = threadIdx.x + GGN_KEEP * blockDim.x; i < gs; i += blockDim.x) {
-        const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
-        out[t * inner + base + i] = tq_from_float<TO>(v * rs * tq_to_float(w[base + i]));
+        float v = (gate_after ? yr[i] : yr[i] * silu(zr[i])) * rs * (w ? tq_to_float(w[base + i]) : 1.0f);
+        if (gate_after) v *= silu(zr[i]);
+        out[t * inner + base + i] = tq_from_float<TO>(v);
     }
 }
 
 TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int z_off, const void* w, int w_dtype,
-                                  void* out, int out_dtype, int T_, int inner, int norm_groups, float eps,
+                                  void* out, int out_dtype, int T_, int inner, int norm_groups, float eps, int gate_after,
                                   cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(inner >= 1 && norm_groups >= 1 && inner % norm_groups == 0 && norm_groups <= 65535,
@@ -357,10 +368,61 @@ TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int 
     TQ_REQUIRE(z_off >= 0 && z_off + inner <= P, "gated_group_norm: the gate lies outside the projection");
     const int gs = inner / norm_groups;
     dim3 grid(T_, norm_groups);
-    const int threads = gs >= 1024 ? 256 : 128;
+    const int threads = gs >= 1024 ? 256 : (gs >= 128 ? 128 : (gs >= 64 ? 64 : 32));
+    if (w == nullptr) w_dtype = TQ_F32;
     TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(grid, threads, 0, stream)(gated_group_norm_kernel<TW, TO>, y, proj, P, z_off, (const TW*)w, (TO*)out,
-                                             inner, gs, eps))));
+                                             inner, gs, eps, gate_after))));
     TQ_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// What a retention layer's recurrence reads, from a fused projection (fp32 rows of P floats): per token the row
+// [v | k' | q'] with k' = rotate(k) * k_scale and q' = rotate(q) (the first rot_dims elements of each head, pairs of
+// neighbours or of halves, angle = position * freq[i] in fp32).  q, k: heads x dk from q_off, k_off; v: heads x dv
+// from v_off.  The row is the layout of the recurrence's input with one group per head: x = v, B = k', C = q'.
+// One block per token, a warp per head.
+// ---------------------------------------------------------------------------------------
+#define RET_MAX_DIM 256
+__global__ void __launch_bounds__(128)
+retention_prepare_kernel(const float* __restrict__ proj, int P, int q_off, int k_off, int v_off, float* __restrict__ out,
+                         const float* __restrict__ freq, int rot_dims, int halves, float k_scale,
+                         const int* __restrict__ positions, int heads, int dk, int dv) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float s_head[4][RET_MAX_DIM];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = proj + (size_t)t * P;
+    const int C = heads * dv + 2 * heads * dk;
+    float* dst = out + (size_t)t * C;
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < heads * dv; i += blockDim.x) dst[i] = row[v_off + i];
+    for (int item = warp; item < 2 * heads; item += 4) {
+        const bool is_q = item >= heads;
+        const int h = is_q ? item - heads : item;
+        const float* src = row + (is_q ? q_off : k_off) + (size_t)h * dk;
+        float* sh = s_head[warp];
+        __syncwarp();
+        for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+        __syncwarp();
+        float* o = dst + heads * dv + (is_q ? heads * dk : 0) + (size_t)h * dk;
+        const float f = is_q ? 1.0f : k_scale;
+        for (int e = lane; e < dk; e += 32) o[e] = tq_rotated(sh, e, rot_dims, halves, freq, pos) * f;
+    }
+}
+
+TQ_EXPORT int tq_retention_prepare(const float* proj, int P, int q_off, int k_off, int v_off, float* out, const float* freq,
+                                   int rot_dims, int halves, float k_scale, const int* positions, int T_, int heads,
+                                   int dk, int dv, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && dk >= 1 && dk <= RET_MAX_DIM && dv >= 1, "retention_prepare: bad sizes %d %d %d", heads, dk, dv);
+    TQ_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + heads * dk <= P && k_off + heads * dk <= P && v_off + heads * dv <= P,
+               "retention_prepare: the heads lie outside the projection's rows of %d", P);
+    TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
+               "retention_prepare: %d rotated elements of a head of %d", rot_dims, dk);
+    tq_launch(T_, 128, 0, stream)(retention_prepare_kernel, proj, P, q_off, k_off, v_off, out, freq, rot_dims, halves, k_scale,
+                                  positions, heads, dk, dv);
+    TQ_CHECK_LAUNCH("retention_prepare");
     return 0;
 }

@@ -67,20 +67,28 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-class Glu:
-    """A gated activation: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(slope * g) * (u + offset).
-    limit 0 means no caps; (0, 1, 0) is silu(gate) * up."""
+GLU_SIGMOID, GLU_GELU_TANH = 0, 1       # csrc/common.cuh TQ_GLU_SIGMOID, TQ_GLU_GELU_TANH
 
-    def __init__(self, limit: float = 0.0, slope: float = 1.0, offset: float = 0.0):
+
+class Glu:
+    """A gated activation: g = min(gate, limit), u = clamp(up, -limit, limit); act(g) * (u + offset) with
+    act(g) = g * sigmoid(slope * g) (kind GLU_SIGMOID), or the tanh form of gelu (kind GLU_GELU_TANH; the slope is not
+    used).  limit 0 means no caps; (0, 1, 0) is silu(gate) * up.  The fused epilogues of the expert products know
+    the sigmoid kind only."""
+
+    def __init__(self, limit: float = 0.0, slope: float = 1.0, offset: float = 0.0, kind: int = GLU_SIGMOID):
         if limit < 0.0:
             raise ValueError(f"a gated activation's caps must not be negative, got {limit}")
-        self.limit, self.slope, self.offset = float(limit), float(slope), float(offset)
+        if kind not in (GLU_SIGMOID, GLU_GELU_TANH):
+            raise ValueError(f"a gated activation's kind must be GLU_SIGMOID or GLU_GELU_TANH, got {kind}")
+        self.limit, self.slope, self.offset, self.kind = float(limit), float(slope), float(offset), int(kind)
 
     def __repr__(self):
-        return f"Glu(limit={self.limit}, slope={self.slope}, offset={self.offset})"
+        return f"Glu(limit={self.limit}, slope={self.slope}, offset={self.offset}, kind={self.kind})"
 
 
 SILU_GLU = Glu()
+GELU_TANH_GLU = Glu(kind=GLU_GELU_TANH)
 
 
 def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, glu: Glu = SILU_GLU) -> torch.Tensor:
@@ -88,8 +96,54 @@ def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, glu: Glu = SILU_GLU) -> to
     T, I = out.shape
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_glu_mul(ptr(gate_up), c_int(code(gate_up.dtype)), ptr(out), c_int(code(out.dtype)),
-                               c_int(T), c_int(I), c_float(glu.limit), c_float(glu.slope), c_float(glu.offset), stream()))
+                               c_int(T), c_int(I), c_float(glu.limit), c_float(glu.slope), c_float(glu.offset),
+                               c_int(glu.kind), stream()))
     return out
+
+
+def mean_of_norms(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float,
+                  out: torch.Tensor) -> torch.Tensor:
+    """out = (a / rms(a) * wa + b / rms(b) * wb) / 2 row by row in float32: two branches, each under an RMS norm of its
+    own, averaged.  a, b, out float32 [R, H]."""
+    for t, what in ((a, "the first branch"), (b, "the second branch"), (out, "the mean")):
+        want_f32(t, what)
+    if a.shape != b.shape or out.shape != a.shape or wa.dtype != wb.dtype:
+        raise KernelError("mean_of_norms: the branches, their weights and the output must agree")
+    R, H = a.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_mean_of_norms(ptr(a), ptr(wa), ptr(b), ptr(wb), c_int(code(wa.dtype)), ptr(out), c_int(R), c_int(H),
+                                     c_float(eps), stream()))
+    return out
+
+
+def glu_table_rows(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, col0: int, out: torch.Tensor,
+                   glu: Glu = SILU_GLU) -> torch.Tensor:
+    """out[t, j] = glu(z[t, j], table[tokens[t], col0 + j]): a gated activation whose second operand is a slice of
+    each token's row of a table.  z float32 [T, D]; out [T, D]."""
+    want_f32(z, "the gate")
+    want_int32(tokens, "tokens")
+    T, D = z.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_glu_table_rows(ptr(z), ptr(tokens), ptr(table), c_int(code(table.dtype)), c_int(table.shape[1]),
+                                      c_int(col0), ptr(out), c_int(code(out.dtype)), c_int(T), c_int(D),
+                                      c_int(table.shape[0]), c_float(glu.limit), c_float(glu.slope), c_float(glu.offset),
+                                      c_int(glu.kind), stream()))
+    return out
+
+
+def scale_bias_cols(x: torch.Tensor, scale: float = 1.0, bias: Optional[torch.Tensor] = None,
+                    cols: Optional[int] = None) -> torch.Tensor:
+    """x[t, j] = x[t, j] * scale + bias[j] in place for the first `cols` columns (all by default) of float32 rows."""
+    want_f32(x, "the rows")
+    T, S = x.shape
+    N = S if cols is None else int(cols)
+    if bias is not None:
+        want_f32(bias, "the bias")
+        if bias.numel() != N:
+            raise KernelError("scale_bias_cols: one bias per column")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_scale_bias_cols(ptr(x), ptr(bias), c_float(scale), c_int(T), c_int(N), c_int(S), stream()))
+    return x
 
 
 def gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, out: torch.Tensor) -> torch.Tensor:

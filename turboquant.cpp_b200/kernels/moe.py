@@ -20,9 +20,11 @@ def align_chunk(n_pairs: int) -> int:
 
 def router_topk(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top_k: int,
                 renorm: bool, ids: torch.Tensor, weights: torch.Tensor,
-                shared_scale: Optional[torch.Tensor]) -> None:
+                shared_scale: Optional[torch.Tensor], logit_bias: Optional[torch.Tensor] = None) -> None:
     """ids/weights [T, k] of the k most probable experts of each token; shared_scale [T] =
-    sigmoid(w_shared_gate . x) when a shared gate is given."""
+    sigmoid(w_shared_gate . x) when a shared gate is given.  logit_bias float32 [E]: added to the experts' logits."""
+    if logit_bias is not None:
+        want_f32(logit_bias, "the logits' bias")
     T, H = x.shape
     E = w_router.shape[0]
     want_int32(ids, "expert ids")
@@ -33,7 +35,8 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_router_topk(ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate),
                                    c_int(code(w_router.dtype)), ptr(logits), ptr(ids), ptr(weights), ptr(shared_scale),
-                                   c_int(T), c_int(H), c_int(E), c_int(top_k), c_int(1 if renorm else 0), stream()),
+                                   c_int(T), c_int(H), c_int(E), c_int(top_k), c_int(1 if renorm else 0),
+                                   ptr(logit_bias), stream()),
           kernels=2)
 
 
@@ -50,8 +53,11 @@ def router_select(logits: torch.Tensor, top_k: int, renorm: bool, ids: torch.Ten
 
 
 def router_logits(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor],
-                  logits: torch.Tensor) -> torch.Tensor:
-    """logits [T, E + 1] float32: x . w_router rows, and in column E x . w_shared_gate (if given), summed in float32."""
+                  logits: torch.Tensor, logit_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """logits [T, E + 1] float32: x . w_router rows (plus logit_bias float32 [E], if given), and in column E
+    x . w_shared_gate (if given), summed in float32."""
+    if logit_bias is not None:
+        want_f32(logit_bias, "the logits' bias")
     T, H = x.shape
     E = w_router.shape[0]
     want_f32(logits, "router logits")
@@ -59,7 +65,8 @@ def router_logits(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Option
         w_shared_gate = w_shared_gate.to(w_router.dtype)
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_router_logits(ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate),
-                                     c_int(code(w_router.dtype)), ptr(logits), c_int(T), c_int(H), c_int(E), stream()))
+                                     c_int(code(w_router.dtype)), ptr(logits), c_int(T), c_int(H), c_int(E),
+                                     ptr(logit_bias), stream()))
     return logits
 
 
@@ -137,11 +144,15 @@ def _counter(device: torch.device) -> torch.Tensor:
 def router_small(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top_k: int,
                  renorm: bool, ids: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
                  layout: ExpertLayout, x_rows: torch.Tensor, correction: Optional[torch.Tensor] = None,
-                 corrected: bool = False, floor: float = 0.0, n_groups: int = 1, keep_groups: int = 1) -> None:
+                 corrected: bool = False, floor: float = 0.0, n_groups: int = 1, keep_groups: int = 1,
+                 logit_bias: Optional[torch.Tensor] = None) -> None:
     """For steps of few tokens: router, expert-sorted layout and the sorted copies of the token rows
     (x_rows[row] = x[token of that row]) in one launch.  Launches on one device must not overlap (they share
     the counter that tells the last block its turn).  corrected: the selection of router_select_corrected
-    (correction [E] float32 or None, groups, floor); it needs n_experts + n_groups <= hidden."""
+    (correction [E] float32 or None, groups, floor); it needs n_experts + n_groups <= hidden.  logit_bias float32
+    [E]: added to the experts' logits before anything else looks at them."""
+    if logit_bias is not None:
+        want_f32(logit_bias, "the logits' bias")
     T, H = x.shape
     E = w_router.shape[0]
     want_int32(ids, "expert ids")
@@ -156,7 +167,7 @@ def router_small(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optiona
         ptr(lo.row_of_pair), ptr(lo.expert_offset), ptr(lo.tile_expert), ptr(lo.tile_row0), ptr(lo.tile_count),
         ptr(lo.n_tiles), ptr(x_rows), ptr(_counter(x.device)), c_int(T), c_int(H), c_int(E), c_int(top_k),
         c_int(1 if renorm else 0), ptr(correction), c_int(1 if corrected else 0), c_float(floor), c_int(n_groups),
-        c_int(keep_groups), stream()))
+        c_int(keep_groups), ptr(logit_bias), stream()))
 
 
 def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:

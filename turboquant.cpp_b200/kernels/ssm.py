@@ -35,14 +35,30 @@ def conv_silu(proj: torch.Tensor, off: int, weight: torch.Tensor, bias: Optional
     return out
 
 
-def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
-             d_skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, heads: int, vdim: int, n_state: int,
-             groups: int, cu_seqlens: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+def ssm_scan(xbc: torch.Tensor, proj: Optional[torch.Tensor], dt_off: int, dt_bias: Optional[torch.Tensor],
+             a_log: Optional[torch.Tensor], d_skip: Optional[torch.Tensor], state: torch.Tensor, y: torch.Tensor, heads: int,
+             vdim: int, n_state: int, groups: int, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+             fixed_decay: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence over every sequence's run of new tokens.  xbc float32 [T, heads*vdim + 2*groups*n_state]
     (x | B | C after convolution and silu); the raw step sizes are proj[:, dt_off:dt_off+heads];
-    state float32 [max_slots, heads, vdim, n_state] (a head's state column by column; rows may be strided); y float32 [T, heads*vdim]."""
-    for t, what in ((xbc, "x, B and C"), (proj, "the projection"), (state, "the state"), (y, "the output")):
+    state float32 [max_slots, heads, vdim, n_state] (a head's state column by column; rows may be strided); y float32 [T, heads*vdim].
+    fixed_decay float32 [heads]: S <- fixed_decay[h] S + B x^T, y = S^T C instead (a constant decay per head, a step
+    size of one, no skip term); proj and the per-head tensors are then not read and may be None."""
+    for t, what in ((xbc, "x, B and C"), (state, "the state"), (y, "the output")):
         want_f32(t, what)
+    if fixed_decay is not None:
+        want_f32(fixed_decay, "the decays")
+        if fixed_decay.numel() != heads:
+            raise KernelError("ssm_scan: one decay per head")
+        lib = load_kernel(_LIB)
+        if tuple(state.shape[1:]) != (heads, vdim, n_state) or not state[0].is_contiguous():
+            raise KernelError("ssm_scan: the state must be [slots, heads, vdim, state] with dense rows")
+        check(_LIB, lib.tq_ssm_scan(ptr(xbc), c_int(xbc.shape[1]), None, c_int(0), c_int(0), None, None, None, c_int(0),
+                                    ctypes_ptr(state), c_longlong(state.stride(0)), ptr(y), c_int(cu_seqlens.shape[0] - 1),
+                                    c_int(heads), c_int(vdim), c_int(n_state), c_int(groups), ptr(cu_seqlens), ptr(slots),
+                                    ptr(fixed_decay), stream()))
+        return y
+    want_f32(proj, "the projection")
     if not (dt_bias.dtype == a_log.dtype == d_skip.dtype):
         raise KernelError("ssm_scan: the per-head constants must share a dtype")
     if tuple(state.shape[1:]) != (heads, vdim, n_state) or not state[0].is_contiguous():
@@ -51,19 +67,45 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.
     check(_LIB, lib.tq_ssm_scan(ptr(xbc), c_int(xbc.shape[1]), ptr(proj), c_int(proj.shape[1]), c_int(dt_off), ptr(dt_bias),
                                 ptr(a_log), ptr(d_skip), c_int(code(dt_bias.dtype)), ctypes_ptr(state),
                                 c_longlong(state.stride(0)), ptr(y), c_int(cu_seqlens.shape[0] - 1), c_int(heads), c_int(vdim),
-                                c_int(n_state), c_int(groups), ptr(cu_seqlens), ptr(slots), stream()))
+                                c_int(n_state), c_int(groups), ptr(cu_seqlens), ptr(slots), None, stream()))
     return y
 
 
-def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: torch.Tensor, norm_groups: int, eps: float,
-                     out: torch.Tensor) -> torch.Tensor:
+MAX_ROTATED_HEAD = 256      # csrc/ssm.cu RET_MAX_DIM
+
+
+def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor,
+                      freq: Optional[torch.Tensor], rot_dims: int, halves: bool, k_scale: float, positions: torch.Tensor,
+                      heads: int, dk: int, dv: int) -> torch.Tensor:
+    """out[t] = [v | rotate(k) * k_scale | rotate(q)] (float32 [T, heads*dv + 2*heads*dk]) from a fused projection's
+    float32 rows: the input of `ssm_scan` with one group per head (x = v, B = k, C = q).  The first rot_dims elements
+    of each head of q and k turn by position * freq[i] (float32 [rot_dims / 2]), pairs of neighbours or of halves."""
+    want_f32(proj, "the projection")
+    want_f32(out, "the recurrence's input")
+    want_int32(positions, "positions")
+    if freq is not None:
+        want_f32(freq, "frequencies")
+    T = proj.shape[0]
+    if out.shape != (T, heads * dv + 2 * heads * dk):
+        raise KernelError("retention_prepare: the output must be [T, heads*dv + 2*heads*dk]")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_retention_prepare(ptr(proj), c_int(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), ptr(out),
+                                         ptr(freq), c_int(rot_dims), c_int(1 if halves else 0), c_float(k_scale),
+                                         ptr(positions), c_int(T), c_int(heads), c_int(dk), c_int(dv), stream()))
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: Optional[torch.Tensor], norm_groups: int,
+                     eps: float, out: torch.Tensor, gate_after: bool = False) -> torch.Tensor:
     """out = rms_in_groups(y * silu(z)) * weight with z = proj[:, z_off:z_off+inner]: the gate first, then each of
-    the norm_groups equal parts of a row divided by its own root mean square."""
+    the norm_groups equal parts of a row divided by its own root mean square.  gate_after: the norm first, then the
+    gate: rms_in_groups(y) * weight * silu(z).  weight None: no weight."""
     want_f32(y, "the recurrence's output")
     want_f32(proj, "the projection")
     T, inner = y.shape
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_gated_group_norm(ptr(y), ptr(proj), c_int(proj.shape[1]), c_int(z_off), ptr(weight),
-                                        c_int(code(weight.dtype)), ptr(out), c_int(code(out.dtype)), c_int(T), c_int(inner),
-                                        c_int(norm_groups), c_float(eps), stream()))
+                                        c_int(code(weight.dtype) if weight is not None else 0), ptr(out),
+                                        c_int(code(out.dtype)), c_int(T), c_int(inner), c_int(norm_groups), c_float(eps),
+                                        c_int(1 if gate_after else 0), stream()))
     return out

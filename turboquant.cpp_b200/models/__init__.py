@@ -3,3 +3,4 @@ from .decoder import DecoderModel, Embedding, LMHead, PairEmbedding, ScheduleEnt
 from .qwen2_moe import Qwen2MoeModel
 from .nuforax import NuforaxModel
 from .lumevik import LumevikModel
+from .sisepel import SisepelModel

@@ -100,10 +100,10 @@ class PairEmbedding(Embedding):
 
 class LMHead(Part):
     """logits = W x in float32; ``name`` may be the embedding's tensor (tied weights:
-    src/engine/tq_model.c:1499-1516)."""
+    src/engine/tq_model.c:1499-1516).  `scale`: a factor on the float32 logits."""
 
-    def __init__(self, name: str, vocab: int, hidden: int):
-        self.name, self.vocab, self.hidden = name, int(vocab), int(hidden)
+    def __init__(self, name: str, vocab: int, hidden: int, scale: float = 1.0):
+        self.name, self.vocab, self.hidden, self.scale = name, int(vocab), int(hidden), float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -112,8 +112,12 @@ class LMHead(Part):
     def bind(self, store: WeightStore) -> None:
         self.weight = store.get(self.name)
 
+    def kernels(self) -> List[str]:
+        return ["elementwise"] if self.scale != 1.0 else []
+
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
-        return linear(xn, self.weight, out_dtype=torch.float32)
+        logits = linear(xn, self.weight, out_dtype=torch.float32)
+        return logits if self.scale == 1.0 else K.scale_bias_cols(logits, self.scale)
 
     def step_work(self, n_tokens, kv_tokens):
         w = self.weight

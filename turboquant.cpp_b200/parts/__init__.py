@@ -4,11 +4,14 @@ from .base import (KVNeed, StateNeed, LayerCache, StepContext, Part, Norm, Posit
                    make_mixer, make_feed_forward, make_norm, make_position_encoding,
                    MIXERS, FEED_FORWARDS, NORMS, POSITION_ENCODINGS)
 from .norm import RMSNorm
-from .rotary import RotaryEncoding, ScaledRotaryEncoding
+from .rotary import RotaryEncoding, ScaledRotaryEncoding, BandRotaryEncoding
 from .attention import AttentionMixer
 from .latent_attention import LatentAttentionMixer
 from .bias_attention import BiasedWindowAttentionMixer
 from .ssm import Mamba2Mixer
+from .retention import RetentionMixer
+from .parallel import ParallelMixer
+from .token_side import TokenSideInput
 from .dense_ffn import SwiGLUFeedForward, ReluSquaredFeedForward, GluFeedForward
 from .moe_ffn import MoEFeedForward
-from .block import PreNormBlock, PostNormBlock
+from .block import PreNormBlock, PostNormBlock, SandwichBlock

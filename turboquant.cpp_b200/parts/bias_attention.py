@@ -17,6 +17,11 @@ is a sink of score 0: the kernels take a sink per head, here zeros.  Value mixin
 a model that mixes keeps its values under a name in the step's `carry`; every later one turns its own into
 (1 - lambda) v + lambda v_first before they are cached, lambda being the layer's scalar tensor `vmix`.
 A position's cache row is [k | v] per key/value head (one plane).
+
+Options other designs use: a rotation of queries and keys (`position`: an encoding that gives float32 frequencies, the
+first `dims` elements of each head), a unit norm on every query and key head after it (`unit_eps` > 0: the head divided
+by sqrt(mean(head^2) + unit_eps), no weight), a cap on the scaled score (`softcap` > 0: s <- softcap * tanh(s / softcap),
+before any bias), and a learned sink per head (`sink_name`: the tensor's name below the prefix) instead of the zero one.
 """
 from __future__ import annotations
 
@@ -49,7 +54,8 @@ class BiasedWindowAttentionMixer(Mixer):
 
     def __init__(self, prefix: str, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                  window: int = 0, keep_first: int = 0, bias_rows: int = 0, bias_far: int = 0, sink: bool = True,
-                 mix_values: Optional[str] = None, mix_first: bool = False):
+                 mix_values: Optional[str] = None, mix_first: bool = False, position=None, unit_eps: float = 0.0,
+                 softcap: float = 0.0, sink_name: Optional[str] = None):
         """bias_rows: rows of the bias table `rel` (0: no bias; -1: as many as the stored tensor has); bias_far: the
         distance from which all share the last row.  mix_values: the name under which the model's mixing layers share values in a step's carry (None: this
         layer does not mix); mix_first: this layer is the one that provides them."""
@@ -57,6 +63,13 @@ class BiasedWindowAttentionMixer(Mixer):
             raise ValueError(f"attention '{prefix}': {heads} heads are not a multiple of {kv_heads} key/value heads")
         if not (1 <= dim <= KB.MAX_DIM and 1 <= vdim <= KB.MAX_DIM):
             raise ValueError(f"attention '{prefix}': key size {dim} and value size {vdim} must be in 1..{KB.MAX_DIM}")
+        if unit_eps < 0.0 or softcap < 0.0:
+            raise ValueError(f"attention '{prefix}': the unit norm's eps {unit_eps} and the cap {softcap} must not be negative")
+        if position is not None and (not hasattr(position, "freq") or position.dims > dim):
+            raise ValueError(f"attention '{prefix}': the position encoding must give frequencies for at most {dim} elements")
+        if (position is not None or unit_eps > 0.0) and mix_values is not None:
+            raise ValueError(f"attention '{prefix}': mixed values come without rotation and unit norm")
+        self.position, self.unit_eps, self.softcap, self.sink_name = position, float(unit_eps), float(softcap), sink_name
         if window < 0 or keep_first < 0:
             raise ValueError(f"attention '{prefix}': negative window {window} or kept positions {keep_first}")
         if bias_rows > 0:
@@ -64,7 +77,7 @@ class BiasedWindowAttentionMixer(Mixer):
         self.prefix, self.hidden = prefix, int(hidden)
         self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
         self.scale, self.window, self.keep_first = float(scale), int(window), int(keep_first) if window else 0
-        self.bias_rows, self.bias_far, self.has_sink = int(bias_rows), int(bias_far), bool(sink)
+        self.bias_rows, self.bias_far, self.has_sink = int(bias_rows), int(bias_far), bool(sink) or sink_name is not None
         self.mix_values, self.mix_first = mix_values, bool(mix_first)
         self.q_size, self.k_size, self.v_size = heads * dim, kv_heads * dim, kv_heads * vdim
         self.w_qkv = self.w_o = self.bias = self.bias_t = self.sink = None
@@ -84,6 +97,8 @@ class BiasedWindowAttentionMixer(Mixer):
             specs.append(WeightSpec(p + "rel", (self.bias_rows, self.heads)))
         if self.mix_values is not None:
             specs.append(WeightSpec(p + "vmix", ()))
+        if self.sink_name is not None:
+            specs.append(WeightSpec(p + self.sink_name, (self.heads,)))
         return specs
 
     def bind(self, store: WeightStore) -> None:
@@ -99,8 +114,12 @@ class BiasedWindowAttentionMixer(Mixer):
             index = torch.tensor(distance_buckets(rel.shape[0], self.bias_far), dtype=torch.long, device=rel.device)
             self.bias = rel[index].contiguous()                                  # [far + 1, heads], a row per distance
             self.bias_t = self.bias.t().contiguous()                             # [heads, far + 1] for the kernel for runs
-        if self.has_sink:
+        if self.sink_name is not None:
+            self.sink = store.get(p + self.sink_name).float().contiguous()
+        elif self.has_sink:
             self.sink = torch.zeros(self.heads, dtype=torch.float32, device=store.device)
+        if self.position is not None:
+            self.position.prepare(store.device)
         if self.mix_values is not None:
             self.mix = float(store.get(p + "vmix").float().item())
 
@@ -118,9 +137,17 @@ class BiasedWindowAttentionMixer(Mixer):
         return {"matmul": (wb(self.w_qkv) + wb(self.w_o), 2.0 * n_tokens * proj),
                 "attn": (float((self.k_size + self.v_size) * el * seen), 2.0 * self.heads * (self.dim + self.vdim) * seen)}
 
-    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+    def input_weight(self) -> torch.Tensor:
+        """The fused input projection's weight [q | k | v rows, hidden]: a mixer that runs this one beside another
+        on the same input may compute both projections as one product and hand the rows over (`projected`)."""
+        return self.w_qkv
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache, projected: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """projected: float32 rows that begin with this mixer's [q | k | v] (the rows may be longer); needs the rotating writer."""
         T, act, dev = xn.shape[0], ctx.act_dtype, xn.device
-        qkv = linear(xn, self.w_qkv, out_dtype=torch.float32)
+        if projected is not None and self.position is None and self.unit_eps == 0.0:
+            raise ValueError(f"attention '{self.prefix}': rows of a wider projection need the rotating writer")
+        qkv = projected if projected is not None else linear(xn, self.w_qkv, out_dtype=torch.float32)
         q = torch.empty((T, self.heads, self.dim), dtype=act, device=dev)
         keep = other = None
         if self.mix_values is not None:
@@ -131,13 +158,19 @@ class BiasedWindowAttentionMixer(Mixer):
                 if other is None or other.shape != (T, self.v_size):
                     raise RuntimeError(f"attention '{self.prefix}': no values of {self.v_size} elements to mix with "
                                        f"were handed on by an earlier layer of this step")
-        KB.kv_write(qkv, q, cache.kv if cache.writes else None, keep, other, self.mix, ctx.positions, ctx.seq_of_token,
-                    cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
+        if self.position is not None or self.unit_eps > 0.0:
+            pe = self.position
+            KB.kv_write_rot(qkv, q, cache.kv if cache.writes else None, pe.freq if pe is not None and pe.dims else None,
+                            pe.dims if pe is not None else 0, pe is not None and pe.halves, self.unit_eps, ctx.positions,
+                            ctx.seq_of_token, cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
+        else:
+            KB.kv_write(qkv, q, cache.kv if cache.writes else None, keep, other, self.mix, ctx.positions, ctx.seq_of_token,
+                        cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
         o = torch.empty((T, self.heads * self.vdim), dtype=act, device=dev)
         if ctx.max_q_len >= self.RUNS_MIN and KB.runs_usable(act, self.dim, self.vdim, cache.page_size):
             KB.attention_runs(q, cache.kv, self.bias_t, self.sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table,
                               cache.page_size, self.window, self.keep_first, self.scale, o, ctx.n_seqs, ctx.max_q_len,
-                              self.heads, self.kv_heads, self.dim, self.vdim)
+                              self.heads, self.kv_heads, self.dim, self.vdim, softcap=self.softcap)
         else:
             longest = min(self.window + self.keep_first, ctx.max_kv_len) if self.window else ctx.max_kv_len
             per_kv = self.heads // self.kv_heads
@@ -148,7 +181,8 @@ class BiasedWindowAttentionMixer(Mixer):
                 blocks, unit = self.kv_heads * -(-per_kv // 16), 16
             KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                          cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
-                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev, unit), bias_t=self.bias_t)
+                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev, unit), bias_t=self.bias_t,
+                         softcap=self.softcap)
         if KG.pays(o, self.w_o):                   # a few tokens: the output projection as a stream of its weights
             return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
         return linear(o, self.w_o, out_dtype=torch.float32)

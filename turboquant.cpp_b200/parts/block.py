@@ -106,3 +106,63 @@ class PostNormBlock(Block):
         y = self.ffn.forward(x if exact else h, ctx)
         self.ffn_norm.add_normed(x, y)
         return x, None
+
+
+class SandwichBlock(Block):
+    """x += post_norm(mixer(pre_norm(x))); x += post_norm(feed_forward(pre_norm(x))): a norm before and one after each
+    sub-layer.  The feed-forward (with its two norms) may be absent.  `after`: parts that change the stream once
+    the sub-layers have run (`apply(x, ctx)`, e.g. a per-layer token input).  The stream stays float32."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, mixer_post: Norm, ffn_norm: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None, ffn_post: Optional[Norm] = None, after=()):
+        if len({ffn is None, ffn_norm is None, ffn_post is None}) != 1:
+            raise ValueError("a feed-forward and its two norms come together")
+        self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
+        self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
+        self.after = list(after)
+
+    def parts(self):
+        own = [self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post] + self.after
+        out = []
+        for p in own:
+            if p is not None:
+                out.append(p)
+                out += p.parts() if hasattr(p, "parts") else []
+        return out
+
+    def _direct(self):
+        return [p for p in [self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post] + self.after
+                if p is not None]
+
+    def cache_need(self) -> Optional[KVNeed]:
+        return self.mixer.cache_need()
+
+    def state_need(self) -> Optional[StateNeed]:
+        return self.mixer.state_need()
+
+    def capturable(self) -> bool:
+        return self.mixer.capturable() and (self.ffn is None or self.ffn.capturable())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self._direct() for s in p.weight_specs()]
+
+    def bind(self, store: WeightStore) -> None:
+        for p in self._direct():
+            p.bind(store)
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"] + [k for p in self._direct() for k in p.kernels()]
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if pending is None:
+            xn = self.mixer_norm.forward(x, ctx.act_dtype)
+        else:                                        # a block of another kind ran before and left its sum open
+            xn = self.mixer_norm.add_forward(x, pending, ctx.act_dtype)
+        self.mixer_post.add_normed(x, self.mixer.forward(xn, ctx, cache))
+        if self.ffn is not None:
+            xn = self.ffn_norm.forward(x, ctx.act_dtype)
+            self.ffn_post.add_normed(x, self.ffn.forward(xn, ctx))
+        for part in self.after:
+            part.apply(x, ctx)
+        return x, None

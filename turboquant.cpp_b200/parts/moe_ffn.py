@@ -13,7 +13,8 @@ order above.  Router logits, softmax and the weighted sum are fp32 on both paths
 Options other designs use: the experts' gated activation as constants (`glu`, `shared_glu`: caps, slope, offset);
 a correction added to the scores for the choice only (`correction`: a tensor of one number per expert); groups of
 neighbouring experts of which only the `keep_groups` best (by their best corrected score) can be chosen; a floor
-added to the chosen scores' sum before the division (`renorm_floor`); the tensors' names (`names`).
+added to the chosen scores' sum before the division (`renorm_floor`); a bias on the experts' logits (`router_bias`:
+a tensor of one number per expert, added before the choice and the weights); the tensors' names (`names`).
 """
 from __future__ import annotations
 
@@ -73,7 +74,7 @@ def shared_rides_with_routed(n_tokens: int, shared_intermediate: int, sms: int) 
 # tensor names below a layer's prefix, as Qwen2 MoE checkpoints have them; {e}: the expert's number
 QWEN_NAMES = {"router": "gate.weight", "expert": "experts.{e}.", "gate": "gate_proj.weight", "up": "up_proj.weight",
               "down": "down_proj.weight", "shared": "shared_expert.", "shared_gate": "shared_expert_gate.weight",
-              "correction": "gate.e_score_correction_bias"}
+              "correction": "gate.e_score_correction_bias", "router_bias": "gate.bias"}
 
 
 class MoEFeedForward(FeedForward):
@@ -90,7 +91,8 @@ class MoEFeedForward(FeedForward):
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
                  norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True,
                  glu: KE.Glu = KE.SILU_GLU, shared_glu: Optional[KE.Glu] = None, correction: bool = False,
-                 n_groups: int = 1, keep_groups: int = 1, renorm_floor: float = 0.0, names=None):
+                 n_groups: int = 1, keep_groups: int = 1, renorm_floor: float = 0.0, names=None,
+                 router_bias: bool = False):
         if n_experts < 1 or not 1 <= top_k <= n_experts:
             raise ValueError(f"experts '{prefix}': top-k {top_k} must be in 1..{n_experts}")
         if n_groups < 1 or n_experts % n_groups or not 1 <= keep_groups <= n_groups \
@@ -98,6 +100,10 @@ class MoEFeedForward(FeedForward):
             raise ValueError(f"experts '{prefix}': {n_experts} experts in {n_groups} groups of which {keep_groups} are "
                              f"kept cannot give {top_k} choices")
         self.glu, self.shared_glu = glu, shared_glu if shared_glu is not None else glu
+        if self.glu.kind != KE.GLU_SIGMOID or self.shared_glu.kind != KE.GLU_SIGMOID:
+            raise ValueError(f"experts '{prefix}': the expert products' fused activation is the sigmoid kind only")
+        self.has_router_bias = bool(router_bias)
+        self.w_router_bias = None
         self.has_correction, self.n_groups, self.keep_groups = bool(correction), int(n_groups), int(keep_groups)
         self.renorm_floor = float(renorm_floor)
         # the choice needs more than the k largest logits: the selection kernel that knows corrections and groups
@@ -119,6 +125,8 @@ class MoEFeedForward(FeedForward):
         specs = [WeightSpec(p + n["router"], (self.n_experts, H))]
         if self.has_correction:
             specs.append(WeightSpec(p + n["correction"], (self.n_experts,)))
+        if self.has_router_bias:
+            specs.append(WeightSpec(p + n["router_bias"], (self.n_experts,)))
         for e in range(self.n_experts):
             q = p + n["expert"].format(e=e)
             specs += [WeightSpec(q + n["gate"], (I, H)), WeightSpec(q + n["up"], (I, H)), WeightSpec(q + n["down"], (H, I))]
@@ -135,6 +143,8 @@ class MoEFeedForward(FeedForward):
         self.w_router = store.get(p + nm["router"])
         if self.has_correction:
             self.w_correction = store.get(p + nm["correction"]).float().contiguous()
+        if self.has_router_bias:
+            self.w_router_bias = store.get(p + nm["router_bias"]).float().contiguous()
         # a tensor stored in 32 bits stays 32-bit: if any of the experts' tensors is kept in float32, the stacked
         # buffers are float32 (the others widen exactly), never the other way round
         names = [p + nm["expert"].format(e=e) + nm[n] for e in range(E) for n in ("gate", "up", "down")]
@@ -291,13 +301,15 @@ class MoEFeedForward(FeedForward):
             # few tokens (decoding): router, layout and the sorted copies of the rows in one launch
             KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows,
                             correction=self.w_correction, corrected=self.corrected, floor=self.renorm_floor,
-                            n_groups=self.n_groups, keep_groups=self.keep_groups)
+                            n_groups=self.n_groups, keep_groups=self.keep_groups, logit_bias=self.w_router_bias)
         else:
             if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
                 # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products
                 # are exact in fp32 and the sum is fp32), then the selection kernel
                 logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
                 KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1), status=ctx.status)
+                if self.w_router_bias is not None:
+                    KE.scale_bias_cols(logits, 1.0, self.w_router_bias, cols=self.n_experts)
                 if self.corrected:
                     KM.router_select_corrected(logits, self.w_correction, k, self.norm_topk, self.renorm_floor,
                                                self.n_groups, self.keep_groups, ids, wts, scale)
@@ -305,11 +317,13 @@ class MoEFeedForward(FeedForward):
                     KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
             elif self.corrected:
                 logits = KM.router_logits(xn, self.w_router, self.w_shared_gate,
-                                          torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev))
+                                          torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev),
+                                          logit_bias=self.w_router_bias)
                 KM.router_select_corrected(logits, self.w_correction, k, self.norm_topk, self.renorm_floor,
                                            self.n_groups, self.keep_groups, ids, wts, scale)
             else:
-                KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
+                KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale,
+                               logit_bias=self.w_router_bias)
             KM.moe_align(ids, layout)
             KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
         if self.ws13 is not None and shared_after and not dual:

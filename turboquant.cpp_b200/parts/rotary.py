@@ -93,3 +93,48 @@ class ScaledRotaryEncoding(PositionEncoding):
 
 
 register_position_encoding("rotary_scaled", ScaledRotaryEncoding)
+
+
+class BandRotaryEncoding(PositionEncoding):
+    """Rotation of the first `dims` elements of a head by angle = position * f_i, f_i = base^(-2i/dims), over pairs of
+    neighbours (2i, 2i+1) or of halves (i, i + dims/2).  With `factor`, frequencies are stretched by wavelength bands:
+    with l = 2 pi / f and the wavelengths `original / high` and `original / low`, short waves (l below the first)
+    keep f, long waves (l above the second) take f / factor, and between the two the blend
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+
+    There is no table over positions and so no longest position: kernels compute the angle in float32 from
+    `freq` (float32 [dims/2] on the device after prepare())."""
+
+    def __init__(self, dims: int, base: float, pairing: str = "neighbours", factor: Optional[float] = None,
+                 low: float = 0.0, high: float = 0.0, original: float = 0.0):
+        if dims % 2 or dims < 0:
+            raise ValueError(f"rotary: {dims} rotated dimensions must be even")
+        if pairing not in ("neighbours", "halves"):
+            raise ValueError(f"rotary: pairing must be 'neighbours' or 'halves', got '{pairing}'")
+        if not base > 0:
+            raise ValueError(f"rotary: base {base} must be positive")
+        self.dims, self.base, self.pairing = int(dims), float(base), pairing
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        if factor is not None:
+            if not (factor > 0 and original > 0 and high > low >= 0):
+                raise ValueError("rotary: factor and original must be positive and high above low")
+            for i, fi in enumerate(f):
+                wave = 2.0 * math.pi / fi
+                if low > 0 and wave > original / low:
+                    f[i] = fi / factor
+                elif wave >= original / high:
+                    s = (original / wave - low) / (high - low)
+                    f[i] = (1.0 - s) * fi / factor + s * fi
+        self._freq64 = torch.tensor(f, dtype=torch.float64)
+        self.freq: Optional[torch.Tensor] = None
+
+    @property
+    def halves(self) -> bool:
+        return self.pairing == "halves"
+
+    def prepare(self, device) -> None:
+        if self.freq is None or self.freq.device != torch.device(device):
+            self.freq = self._freq64.to(torch.float32).to(device).contiguous()
+
+
+register_position_encoding("rotary_bands", BandRotaryEncoding)
