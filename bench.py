@@ -150,9 +150,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
                     "prefill to this file (torch profiler; not part of any timed number)")
-    ap.add_argument("--design", choices=["nuforax", "lumevik"], default="", help="instead of the default workload: prompt and decode "
-                    "speed of this design at layer sizes of a real model (random weights), beside the closest Qwen2 decoder of "
-                    "equal width, depth and heads")
+    ap.add_argument("--design", choices=["nuforax", "lumevik", "sisepel"], default="", help="instead of the default workload: prompt "
+                    "and decode speed of this design at layer sizes of a real model (random weights), beside the closest other "
+                    "decoder of equal width, depth and heads")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of the sizes to run")
     args = ap.parse_args()
     if args.design and args.impl != "reference":
@@ -374,6 +374,28 @@ LUMEVIK_SIZES = {
     "w2048": (2048, 4, 16, 4, 128, 1024, 4, 512, 768, 5632, 60, 4, 1408, 5632, 32768),
 }
 
+def sisepel_config(width, layers, heads, kv_heads, dim, window, r_heads, r_dim, r_vdim, ff, experts, top, e_ff, s_ff, side, vocab):
+    """Layers in pairs: a dense feed-forward, then routed experts; every layer has windowed attention and retention
+    side by side and a token input of its own."""
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                      "mask": {"size": window},
+                      "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+             "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"base": 10000.0, "dims": r_dim},
+                       "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * i / max(1, r_heads - 1)) for i in range(r_heads)]}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": s_ff}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Sisepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+            "token_side": {"dim": side},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
+
+
+SISEPEL_SIZES = {
+    # name: Lumevik's sizes of that name (width, layers, heads, kv heads, head size, window, experts and feed-forwards, vocab)
+    # and, for the parts Lumevik does not have: (retention heads, key size, value size, width of a layer's token input)
+    "w1024": (8, 64, 128, 64),
+    "w2048": (16, 128, 128, 128),
+}
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, dim, rot, vdim, rank, window, ff, ssm heads, ssm vdim, ssm state, ssm groups, vocab)
     "w1024": (1024, 6, 8, 64, 64, 64, 256, 1024, 4096, 32, 64, 64, 1, 32768),
@@ -457,6 +479,8 @@ def design_compare(args) -> int:
 
     if args.design == "lumevik":
         return lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
+    if args.design == "sisepel":
+        return sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
     result = {"metric": "prompt and decode speed, Nuforax beside the dense Qwen2 decoder of equal width", "unit": "tokens/s",
               "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
               "peaks": pk, "sizes": {}}
@@ -518,6 +542,42 @@ def lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, wa
             entry[who] = dict(measure(model, V), config={"width": W, "layers": L, "heads": H, "kv_heads": G, "head_size": D,
                                                          "window": window, "dense_ff": ff, "experts": E, "top": top,
                                                          "expert_ff": e_ff, "shared_ff": s_ff})
+            if args.kernel_table:
+                kernel_table(tq, model, rng, V, 8, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        result["sizes"][name] = entry
+    result["clocks"] = clocks.stop()
+    print(json.dumps(result))
+    return 0
+
+
+def sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup) -> int:
+    """The Sisepel decoder beside the Lumevik decoder of the same width, depth, heads, window, experts and feed-forward
+    sizes: both run windowed attention with a sink on the same kernels and the same expert products; Sisepel adds a
+    retention branch and a token input to every layer and has no latent attention."""
+    import torch
+    result = {"metric": "prompt and decode speed, Sisepel beside the Lumevik decoder of equal sizes", "unit": "tokens/s",
+              "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+              "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.sizes.split(","):
+        if name not in SISEPEL_SIZES:
+            print(json.dumps({"error": f"unknown size '{name}'; known: {sorted(SISEPEL_SIZES)}"}))
+            return 2
+        (W, L, H, G, D, window, keep, rank, q_rank, ff, E, top, e_ff, s_ff, V) = LUMEVIK_SIZES[name]
+        (rh, rd, rv, side) = SISEPEL_SIZES[name]
+        entry = {}
+        for who, cfg in (("sisepel", sisepel_config(W, L, H, G, D, window, rh, rd, rv, ff, E, top, e_ff, s_ff, side, V)),
+                         ("lumevik", lumevik_config(W, L, H, G, D, window, keep, rank, q_rank, ff, E, top, e_ff, s_ff, V))):
+            model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            conf = {"width": W, "layers": L, "heads": H, "kv_heads": G, "head_size": D, "window": window, "dense_ff": ff,
+                    "experts": E, "top": top, "expert_ff": e_ff, "shared_ff": s_ff}
+            if who == "sisepel":
+                conf.update(retention={"heads": rh, "dim": rd, "vdim": rv}, token_input=side)
+            entry[who] = dict(measure(model, V), config=conf)
             if args.kernel_table:
                 kernel_table(tq, model, rng, V, 8, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
             del model

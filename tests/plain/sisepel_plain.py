@@ -104,15 +104,14 @@ def rotate(v, pos, rot, pairing):
 
 
 # ---- the softmax branch ------------------------------------------------------------------------------------------
-def window_attention(h, m, w, p, eps):
-    """Queries and keys are rotated (neighbouring pairs), then made unit length per head; scores are scaled, capped by
-    cap * tanh(score / cap), masked to the last `size` positions, and the softmax's denominator also holds exp(sink)."""
-    T = h.shape[0]
-    H, G, dk, dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
-    q = (h @ w[p + "q"].T).reshape(T, H, dk)
-    k = (h @ w[p + "k"].T).reshape(T, G, dk)
-    v = (h @ w[p + "v"].T).reshape(T, G, dv)
+def attention_core(q, k, v, m, sink, eps):
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv] as projected, positions 0 .. T-1.  Queries and keys are rotated
+    (neighbouring pairs), then made unit length per head; scores are scaled, capped by cap * tanh(score / cap), masked
+    to the last `size` positions, and the softmax's denominator also holds exp(sink) (sink [H], or None)."""
+    T, H, dk = q.shape
+    G, dv = k.shape[1], v.shape[2]
     rot = m.get("rot")
+    q, k = q.copy(), k.copy()
     for t in range(T):
         q[t] = unit(rotate(q[t], t, rot, "neighbours"), eps)
         k[t] = unit(rotate(k[t], t, rot, "neighbours"), eps)
@@ -126,34 +125,50 @@ def window_attention(h, m, w, p, eps):
             s = (k[lo:i + 1, g] @ q[i, a]) * m["scale"]
             if cap:
                 s = cap * np.tanh(s / cap)
-            top = max(s.max(), w[p + "sink"][a]) if (p + "sink") in w else s.max()
+            top = s.max() if sink is None else max(s.max(), sink[a])
             e = np.exp(s - top)
-            den = e.sum() + (math.exp(w[p + "sink"][a] - top) if (p + "sink") in w else 0.0)
+            den = e.sum() + (0.0 if sink is None else math.exp(sink[a] - top))
             out[i, a] = (e / den) @ v[lo:i + 1, g]
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+    return out
+
+
+def window_attention(h, m, w, p, eps):
+    T = h.shape[0]
+    H, G, dk, dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
+    q = (h @ w[p + "q"].T).reshape(T, H, dk)
+    k = (h @ w[p + "k"].T).reshape(T, G, dk)
+    v = (h @ w[p + "v"].T).reshape(T, G, dv)
+    return attention_core(q, k, v, m, w.get(p + "sink"), eps).reshape(T, H * dv) @ w[p + "o"].T
 
 
 # ---- the retention branch ----------------------------------------------------------------------------------------
-def retention(h, m, w, p, eps):
-    """Per head: S <- decay * S + k v^T, o = S^T q, with q and k rotated (halves) and k scaled by dim^(-1/2); o is
-    made unit length per head, gated by silu(W_g h) and projected."""
-    T = h.shape[0]
-    H, dk, dv = m["heads"], m["dim"], m["vdim"]
-    q = (h @ w[p + "q"].T).reshape(T, H, dk)
-    k = (h @ w[p + "k"].T).reshape(T, H, dk)
-    v = (h @ w[p + "v"].T).reshape(T, H, dv)
-    gate = silu(h @ w[p + "g"].T)
+def retention_core(q, k, v, m, S=None, start=0):
+    """q, k [T, H, dk], v [T, H, dv] as projected, at positions start .. start+T-1.  Per head: S <- decay * S + k v^T,
+    o = S^T q, with q and k rotated (halves) and k scaled by dk^(-1/2).  Returns (o [T, H, dv], S [H, dk, dv])."""
+    T, H, dk = q.shape
+    dv = v.shape[2]
     rot = m.get("rot")
-    S = np.zeros((H, dk, dv), dtype=F)
+    S = np.zeros((H, dk, dv), dtype=F) if S is None else S.copy()
     o = np.zeros((T, H, dv), dtype=F)
     for t in range(T):
-        qt = rotate(q[t], t, rot, "halves")
-        kt = rotate(k[t], t, rot, "halves") * dk ** -0.5
+        qt = rotate(q[t], start + t, rot, "halves")
+        kt = rotate(k[t], start + t, rot, "halves") * dk ** -0.5
         for a in range(H):
             S[a] = m["decay"][a] * S[a] + np.outer(kt[a], v[t, a])
             o[t, a] = S[a].T @ qt[a]
+    return o, S
+
+
+def retention(h, m, w, p, eps):
+    """The recurrence's output is made unit length per head, gated by silu(W_g h) and projected."""
+    T = h.shape[0]
+    H, dk, dv = m["heads"], m["dim"], m.get("vdim", m["dim"])
+    q = (h @ w[p + "q"].T).reshape(T, H, dk)
+    k = (h @ w[p + "k"].T).reshape(T, H, dk)
+    v = (h @ w[p + "v"].T).reshape(T, H, dv)
+    o, _ = retention_core(q, k, v, m)
     o = unit(o, eps).reshape(T, H * dv)
-    return (o * gate) @ w[p + "o"].T
+    return (o * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
 def parallel_mixer(h, m, w, p, eps):
@@ -168,21 +183,34 @@ def gated(h, w, p, act):
 
 
 def route(h, ml, w, p):
-    """Logits with a bias; the `top` largest (the lower index wins a tie); weights = softmax over the chosen."""
+    """Logits with a bias; the `top` largest (the lower index wins a tie); weights = softmax over the chosen.
+    Also each row's margin: how far the last chosen expert lies above the best one left out, as probabilities of a
+    softmax over all experts (0 if every expert is chosen)."""
     z = h @ w[p + "router"].T + w[p + "router.b"]
-    ids = np.argsort(-z, axis=-1, kind="stable")[:, :ml["router"]["top"]]
+    top = ml["router"]["top"]
+    order = np.argsort(-z, axis=-1, kind="stable")
+    ids = order[:, :top]
+    prob = np.exp(z - z.max(axis=-1, keepdims=True))
+    prob /= prob.sum(axis=-1, keepdims=True)
+    ranked = np.take_along_axis(prob, order, axis=-1)
+    margins = ranked[:, top - 1] - ranked[:, top] if top < z.shape[1] else np.ones(z.shape[0])
+    return ids, chosen_weights(z, ids), margins
+
+
+def chosen_weights(z, ids):
     zs = np.take_along_axis(z, ids, axis=-1)
     e = np.exp(zs - zs.max(axis=-1, keepdims=True))
-    return ids, e / e.sum(axis=-1, keepdims=True)
+    return e / e.sum(axis=-1, keepdims=True)
 
 
-def experts(h, ml, w, p, ids=None):
-    own_ids, wts = route(h, ml, w, p)
-    if ids is not None:                         # a test may hand in another choice where two logits nearly tie
-        z = h @ w[p + "router"].T + w[p + "router.b"]
-        zs = np.take_along_axis(z, ids, axis=-1)
-        e = np.exp(zs - zs.max(axis=-1, keepdims=True))
-        wts = e / e.sum(axis=-1, keepdims=True)
+def experts(h, ml, w, p, ids=None, record=None):
+    """ids: another choice of experts than the router's own (a test hands it in where two logits nearly tie); the
+    weights are then the softmax over those experts' logits.  record: a list that receives (ids, weights, margins)."""
+    own_ids, wts, margins = route(h, ml, w, p)
+    if record is not None:
+        record.append((own_ids, wts, margins))
+    if ids is not None:
+        wts = chosen_weights(h @ w[p + "router"].T + w[p + "router.b"], ids)
     else:
         ids = own_ids
     y = np.zeros_like(h)
@@ -194,10 +222,10 @@ def experts(h, ml, w, p, ids=None):
     return y
 
 
-def feed_forward(h, ml, w, p, ids=None):
+def feed_forward(h, ml, w, p, ids=None, record=None):
     if ml.get("kind", "dense") == "dense":
         return gated(h, w, p + "mlp.", gelu_tanh)
-    return experts(h, ml, w, p + "mlp.", ids)
+    return experts(h, ml, w, p + "mlp.", ids, record)
 
 
 # ---- per-layer token input ----------------------------------------------------------------------------------------
@@ -214,22 +242,30 @@ class PlainSisepel:
             self.cfg = json.load(f)
         self.w = read_safetensors(os.path.join(folder, "model.safetensors"))
 
-    def forward(self, tokens, routing=None, streams=None):
-        """Logits [T, vocab] of one sequence.  routing: {layer: ids [T, top]} overrides a layer's choice of experts;
-        streams: a list that receives the residual stream after every layer."""
+    def forward(self, tokens, routing=None, forced=None, streams=None):
+        """Logits [T, vocab] of one sequence.  routing: a list that receives (ids, weights, margins) of every routed
+        layer in order; forced: expert choices [T, top] for the first routed layers, taken instead of the router's
+        own; streams: a list that receives the residual stream after every layer."""
         cfg, w = self.cfg, self.w
         eps = cfg["norm"]["eps"]
         tokens = np.asarray(tokens, dtype=np.int64)
         x = w["embed"][tokens].astype(F)
         side = cfg.get("token_side")
+        routed = 0
         for i, layer in enumerate(cfg["layers"]):
             p = f"l{i}."
             if layer["type"] != "parallel":
                 raise ValueError(f"layer type {layer['type']}")
             y = parallel_mixer(norm(x, w[p + "norm1"], eps), layer["mixer"], w, p + "mix.", eps)
             x = x + norm(y, w[p + "norm1b"], eps)
-            if layer.get("mlp") is not None:
-                y = feed_forward(norm(x, w[p + "norm2"], eps), layer["mlp"], w, p, (routing or {}).get(i))
+            ml = layer.get("mlp")
+            if ml is not None:
+                ids = None
+                if ml.get("kind", "dense") == "moe":
+                    if forced is not None and routed < len(forced):
+                        ids = np.asarray(forced[routed])
+                    routed += 1
+                y = feed_forward(norm(x, w[p + "norm2"], eps), ml, w, p, ids, routing)
                 x = x + norm(y, w[p + "norm2b"], eps)
             if side:
                 x = x + token_side(x, tokens, i, side["dim"], w, p + "side.", eps)

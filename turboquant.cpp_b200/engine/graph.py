@@ -116,6 +116,7 @@ class DecodeGraph:
             _call.LAUNCHES = before
             self.graph = g
             return logits
+        self.first_debug = None               # nobody asked for the eager step's records: they are not this step's
         self.graph.replay()
         eng.graphs.replays += 1
         _call.LAUNCHES += self.kernels
