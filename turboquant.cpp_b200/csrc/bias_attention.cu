@@ -80,7 +80,7 @@ TQ_EXPORT int tq_bias_kv_write(const float* qkv, void* q_out, void* cache, int a
 // The same split with a rotation and a unit norm on the way: queries and keys are rotated by their token's position
 // (the first rot_dims elements of each head, pairs of neighbours or of halves, angle = position * freq[i] in fp32), then
 // each head is divided by its root mean square (unit_eps > 0: x / sqrt(mean(x^2) + unit_eps); 0: left as it is).
-// One block per token, a warp per head; values are copied.
+// Grid (token, groups of four query and key heads): a warp per head; the blocks of a token share out the copy of the values.
 // ---------------------------------------------------------------------------------------
 template <typename TA>
 __global__ void __launch_bounds__(128)
@@ -96,38 +96,40 @@ bias_kv_write_rot_kernel(const float* __restrict__ qkv, int row_stride, TA* __re
     const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv, dr = dk + dv;
     const float* row = qkv + (size_t)t * row_stride;
     const int pos = positions[t];
-    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
-    const int page = TQ_CHECKED(table[TQ_CHECKED(pos / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
-    const int slot = pos % page_size;
-    for (int head = warp; head < nh + nkv; head += 4) {
-        const float* src = row + (size_t)head * dk;            // keys follow the queries in the row
-        float* sh = s_head[warp];
-        __syncwarp();
-        for (int e = lane; e < dk; e += 32) sh[e] = src[e];
-        __syncwarp();
-        float v[BA_EPL];
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < BA_EPL; ++j) {
-            const int e = lane + 32 * j;
-            v[j] = e < dk ? tq_rotated(sh, e, rot_dims, halves, freq, pos) : 0.f;
-            ss += v[j] * v[j];
-        }
-        float rs = 1.f;
-        if (unit_eps > 0.f) rs = 1.0f / sqrtf(tq_warp_sum(ss) / (float)dk + unit_eps);
-        TA* dst = head < nh ? q_out + ((size_t)t * nh + head) * dk
-                            : (cache ? cache + (((size_t)page * nkv + (head - nh)) * page_size + slot) * dr : nullptr);
-        if (dst == nullptr) continue;
-#pragma unroll
-        for (int j = 0; j < BA_EPL; ++j) {
-            const int e = lane + 32 * j;
-            if (e < dk) dst[e] = tq_from_float<TA>(v[j] * rs);
-        }
+    int page = 0;                      // without a cache (a layer that only reads another's) no table is looked at
+    if (cache != nullptr) {
+        const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+        page = TQ_CHECKED(table[TQ_CHECKED(pos / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
     }
-    if (cache == nullptr) return;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-        const int g = i / dv, e = i % dv;
-        cache[(((size_t)page * nkv + g) * page_size + slot) * dr + dk + e] = tq_from_float<TA>(row[nq + nk + i]);
+    const int slot = pos % page_size;
+    if (cache != nullptr)
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
+            const int g = i / dv, e = i % dv;
+            cache[(((size_t)page * nkv + g) * page_size + slot) * dr + dk + e] = tq_from_float<TA>(row[nq + nk + i]);
+        }
+    const int head = blockIdx.y * 4 + warp;
+    if (head >= nh + nkv) return;
+    const float* src = row + (size_t)head * dk;                // keys follow the queries in the row
+    float* sh = s_head[warp];
+    for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+    __syncwarp();
+    float v[BA_EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < BA_EPL; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < dk ? tq_rotated(sh, e, rot_dims, halves, freq, pos) : 0.f;
+        ss += v[j] * v[j];
+    }
+    float rs = 1.f;
+    if (unit_eps > 0.f) rs = 1.0f / sqrtf(tq_warp_sum(ss) / (float)dk + unit_eps);
+    TA* dst = head < nh ? q_out + ((size_t)t * nh + head) * dk
+                        : (cache ? cache + (((size_t)page * nkv + (head - nh)) * page_size + slot) * dr : nullptr);
+    if (dst == nullptr) return;
+#pragma unroll
+    for (int j = 0; j < BA_EPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e < dk) dst[e] = tq_from_float<TA>(v[j] * rs);
     }
 }
 
@@ -142,7 +144,7 @@ TQ_EXPORT int tq_bias_kv_write_rot(const float* qkv, int row_stride, void* q_out
     TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
                "bias_kv_write_rot: %d rotated elements of a head of %d", rot_dims, dk);
     TQ_DISPATCH(act_dtype, TA,
-        (tq_launch(T_, 128, 0, stream)(bias_kv_write_rot_kernel<TA>, qkv, row_stride, (TA*)q_out, (TA*)cache, freq, rot_dims,
+        (tq_launch(dim3(T_, (nh + nkv + 3) / 4), 128, 0, stream)(bias_kv_write_rot_kernel<TA>, qkv, row_stride, (TA*)q_out, (TA*)cache, freq, rot_dims,
             halves, unit_eps, positions, seq_of_token, page_table, table_stride, page_size, nh, nkv, dk, dv, n_seqs, n_pages)));
     TQ_CHECK_LAUNCH("bias_kv_write_rot");
     return 0;

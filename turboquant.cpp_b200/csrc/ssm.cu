@@ -359,6 +359,47 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     }
 }
 
+// The same for short parts (up to 32 * GGN_KEEP elements): a warp per part, four parts a block, no block-wide sums.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
+                             const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, int n_groups, float eps,
+                             int gate_after) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, g = blockIdx.y * 4 + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const int base = g * gs;
+    const float* yr = y + t * inner + base;
+    const float* zr = proj + t * P + z_off + base;
+    auto silu = [](float z) { return z / (1.0f + expf(-z)); };
+    float keep[GGN_KEEP], gate[GGN_KEEP];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < GGN_KEEP; ++k) {
+        const int i = lane + 32 * k;
+        keep[k] = 0.f;
+        gate[k] = 0.f;
+        if (i < gs) {
+            gate[k] = silu(zr[i]);
+            keep[k] = gate_after ? yr[i] : yr[i] * gate[k];
+        }
+        ss += keep[k] * keep[k];
+    }
+    ss = tq_warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)gs + eps);
+#pragma unroll
+    for (int k = 0; k < GGN_KEEP; ++k) {
+        const int i = lane + 32 * k;
+        if (i < gs) {
+            float v = keep[k] * rs * (w ? tq_to_float(w[base + i]) : 1.0f);
+            if (gate_after) v *= gate[k];
+            out[t * inner + base + i] = tq_from_float<TO>(v);
+        }
+    }
+}
+
 TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int z_off, const void* w, int w_dtype,
                                   void* out, int out_dtype, int T_, int inner, int norm_groups, float eps, int gate_after,
                                   cudaStream_t stream) {
@@ -370,6 +411,13 @@ TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int 
     dim3 grid(T_, norm_groups);
     const int threads = gs >= 1024 ? 256 : (gs >= 128 ? 128 : (gs >= 64 ? 64 : 32));
     if (w == nullptr) w_dtype = TQ_F32;
+    if (gs <= 32 * GGN_KEEP && norm_groups >= 4) {
+        TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+            (tq_launch(dim3(T_, (norm_groups + 3) / 4), 128, 0, stream)(gated_group_norm_warp_kernel<TW, TO>, y, proj, P, z_off,
+                (const TW*)w, (TO*)out, inner, gs, norm_groups, eps, gate_after))));
+        TQ_CHECK_LAUNCH("gated_group_norm");
+        return 0;
+    }
     TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(grid, threads, 0, stream)(gated_group_norm_kernel<TW, TO>, y, proj, P, z_off, (const TW*)w, (TO*)out,
                                              inner, gs, eps, gate_after))));
@@ -382,7 +430,7 @@ TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int 
 // [v | k' | q'] with k' = rotate(k) * k_scale and q' = rotate(q) (the first rot_dims elements of each head, pairs of
 // neighbours or of halves, angle = position * freq[i] in fp32).  q, k: heads x dk from q_off, k_off; v: heads x dv
 // from v_off.  The row is the layout of the recurrence's input with one group per head: x = v, B = k', C = q'.
-// One block per token, a warp per head.
+// Grid (token, groups of four heads of k and q): a warp per head; the blocks of a token share out the copy of v.
 // ---------------------------------------------------------------------------------------
 #define RET_MAX_DIM 256
 __global__ void __launch_bounds__(128)
@@ -396,20 +444,19 @@ retention_prepare_kernel(const float* __restrict__ proj, int P, int q_off, int k
     const float* row = proj + (size_t)t * P;
     const int C = heads * dv + 2 * heads * dk;
     float* dst = out + (size_t)t * C;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < heads * dv; i += gridDim.y * blockDim.x) dst[i] = row[v_off + i];
+    const int item = blockIdx.y * 4 + warp;              // k heads, then q heads
+    if (item >= 2 * heads) return;
     const int pos = positions[t];
-    for (int i = threadIdx.x; i < heads * dv; i += blockDim.x) dst[i] = row[v_off + i];
-    for (int item = warp; item < 2 * heads; item += 4) {
-        const bool is_q = item >= heads;
-        const int h = is_q ? item - heads : item;
-        const float* src = row + (is_q ? q_off : k_off) + (size_t)h * dk;
-        float* sh = s_head[warp];
-        __syncwarp();
-        for (int e = lane; e < dk; e += 32) sh[e] = src[e];
-        __syncwarp();
-        float* o = dst + heads * dv + (is_q ? heads * dk : 0) + (size_t)h * dk;
-        const float f = is_q ? 1.0f : k_scale;
-        for (int e = lane; e < dk; e += 32) o[e] = tq_rotated(sh, e, rot_dims, halves, freq, pos) * f;
-    }
+    const bool is_q = item >= heads;
+    const int h = is_q ? item - heads : item;
+    const float* src = row + (is_q ? q_off : k_off) + (size_t)h * dk;
+    float* sh = s_head[warp];
+    for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+    __syncwarp();
+    float* o = dst + heads * dv + (is_q ? heads * dk : 0) + (size_t)h * dk;
+    const float f = is_q ? 1.0f : k_scale;
+    for (int e = lane; e < dk; e += 32) o[e] = tq_rotated(sh, e, rot_dims, halves, freq, pos) * f;
 }
 
 TQ_EXPORT int tq_retention_prepare(const float* proj, int P, int q_off, int k_off, int v_off, float* out, const float* freq,
@@ -421,7 +468,8 @@ TQ_EXPORT int tq_retention_prepare(const float* proj, int P, int q_off, int k_of
                "retention_prepare: the heads lie outside the projection's rows of %d", P);
     TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
                "retention_prepare: %d rotated elements of a head of %d", rot_dims, dk);
-    tq_launch(T_, 128, 0, stream)(retention_prepare_kernel, proj, P, q_off, k_off, v_off, out, freq, rot_dims, halves, k_scale,
+    TQ_REQUIRE(heads <= 100000, "retention_prepare: %d heads", heads);
+    tq_launch(dim3(T_, (2 * heads + 3) / 4), 128, 0, stream)(retention_prepare_kernel, proj, P, q_off, k_off, v_off, out, freq, rot_dims, halves, k_scale,
                                   positions, heads, dk, dv);
     TQ_CHECK_LAUNCH("retention_prepare");
     return 0;
