@@ -272,6 +272,28 @@ def test_mean_of_two_normed_branches(R, H, wdtype):
     assert rel(out, want) < 1e-5
 
 
+@pytest.mark.parametrize("R,H", [(1, 36), (3, 256), (7, 1000), (2, 2048), (2, 5000), (5, 37)])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_a_sum_under_a_norm_with_the_next_norm_along(R, H, wdtype, odtype):
+    """x += norm(y), and the norm that reads the new x next in the same pass (both row forms of the kernel: rows of
+    a multiple of four up to 4096 elements, and the rest)."""
+    from turboquant_cpp_b200.kernels import elementwise as KE
+    rng = np.random.default_rng(R * H)
+    x, y = host(dev(rng.standard_normal((R, H)))), host(dev(0.02 * rng.standard_normal((R, H))))
+    w, wn = dev(1 + 0.3 * rng.standard_normal(H), wdtype), dev(1 + 0.3 * rng.standard_normal(H), wdtype)
+    xd = dev(x)
+    copy = torch.empty((R, H), dtype=odtype, device=DEV)
+    nxt = torch.empty((R, H), dtype=odtype, device=DEV)
+    KE.add_rmsnorm(xd, dev(y), w, 1e-5, copy, wn, nxt, 3e-4)
+    want = x + P.norm(y, host(w), 1e-5)
+    tol = 1e-5 if odtype == torch.float32 else 5e-3
+    assert rel(xd, want) < 1e-5 and rel(copy, want) < tol
+    assert rel(nxt, P.norm(want, host(wn), 3e-4)) < tol
+    xd2, nxt2 = dev(x), torch.empty((R, H), dtype=odtype, device=DEV)
+    KE.add_rmsnorm(xd2, dev(y), w, 1e-5, None, wn, nxt2)              # no copy; the following norm with the same eps
+    assert torch.equal(xd2, xd) and rel(nxt2, P.norm(want, host(wn), 1e-5)) < tol
+
+
 @pytest.mark.parametrize("T,D,col0,width", [(1, 24, 0, 24), (9, 6, 12, 30), (40, 1, 3, 4), (5, 130, 130, 390)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gated_slice_of_a_token_table(T, D, col0, width, dtype):

@@ -410,7 +410,8 @@ TQ_EXPORT int tq_embed_pair_rows(const int* tokens, const void* table, const voi
 // ---------------------------------------------------------------------------------------
 template <typename TY, typename TW, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__ y, const TW* __restrict__ w,
-                                   TO* __restrict__ copy, int H, float eps) {
+                                   TO* __restrict__ copy, int H, float eps, const TW* __restrict__ next_w,
+                                   TO* __restrict__ next_out, float next_eps) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
@@ -424,11 +425,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__
     }
     ss = tq_block_sum(ss, scratch);
     const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    float s2 = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = xr[i] + tq_to_float(yr[i]) * rs * tq_to_float(w[i]);
         xr[i] = v;
+        s2 += v * v;
         if (copy) copy[r * H + i] = tq_from_float<TO>(v);
     }
+    if (next_out == nullptr) return;               // the same for the whole block
+    s2 = tq_block_sum(s2, scratch);
+    const float rs2 = 1.0f / sqrtf(s2 / (float)H + next_eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)      // a thread reads back what it wrote itself
+        next_out[r * H + i] = tq_from_float<TO>(xr[i] * rs2 * tq_to_float(next_w[i]));
 }
 
 // The same for float32 y in rows of up to 4 * ADDN_THREADS * NV elements, a multiple of four: a thread keeps its
@@ -437,7 +445,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__
 template <typename TW, typename TO, int NV>
 __global__ void __launch_bounds__(ADDN_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const TW* __restrict__ w,
-                       TO* __restrict__ copy, int H, float eps) {
+                       TO* __restrict__ copy, int H, float eps, const TW* __restrict__ next_w,
+                       TO* __restrict__ next_out, float next_eps) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
@@ -459,6 +468,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const
     }
     ss = tq_block_sum(ss, scratch);
     const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    float s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int i = threadIdx.x + k * ADDN_THREADS;
@@ -469,6 +479,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const
             v.z = xv[k].z + yv[k].z * rs * tq_to_float(w[4 * i + 2]);
             v.w = xv[k].w + yv[k].w * rs * tq_to_float(w[4 * i + 3]);
             xr[i] = v;
+            xv[k] = v;
+            s2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             if (copy) {
                 TO* c = copy + r * H + 4 * i;
                 c[0] = tq_from_float<TO>(v.x); c[1] = tq_from_float<TO>(v.y);
@@ -476,18 +488,36 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const
             }
         }
     }
+    if (next_out == nullptr) return;               // the same for the whole block
+    s2 = tq_block_sum(s2, scratch);
+    const float rs2 = 1.0f / sqrtf(s2 / (float)H + next_eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        if (i < n4) {
+            TO* c = next_out + r * H + 4 * i;
+            c[0] = tq_from_float<TO>(xv[k].x * rs2 * tq_to_float(next_w[4 * i]));
+            c[1] = tq_from_float<TO>(xv[k].y * rs2 * tq_to_float(next_w[4 * i + 1]));
+            c[2] = tq_from_float<TO>(xv[k].z * rs2 * tq_to_float(next_w[4 * i + 2]));
+            c[3] = tq_from_float<TO>(xv[k].w * rs2 * tq_to_float(next_w[4 * i + 3]));
+        }
+    }
 }
 
+// next_w, next_out (optional, in the dtypes of w and of copy): the norm that reads the new x next,
+// next_out[r] = x[r] / sqrt(mean(x[r]^2) + next_eps) * next_w, taken in the same pass.
 TQ_EXPORT int tq_add_rmsnorm(float* x, const void* y, int y_dtype, const void* w, int w_dtype, void* copy,
-                             int copy_dtype, int R, int H, float eps, cudaStream_t stream) {
+                             int copy_dtype, int R, int H, float eps, const void* next_w, void* next_out, float next_eps,
+                             cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0, "add_rmsnorm: bad sizes R=%d H=%d", R, H);
+    TQ_REQUIRE(next_out == nullptr || next_w != nullptr, "add_rmsnorm: a following norm without its weight%s", "");
     if (y_dtype == TQ_F32 && H % 4 == 0 && H <= 4 * ADDN_THREADS * 4 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
         const int nv = (H / 4 + ADDN_THREADS - 1) / ADDN_THREADS;
 #define ADDN_LAUNCH(NV_)                                                                                           \
         TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,                                                       \
             (tq_launch(R, ADDN_THREADS, 0, stream)(add_rmsnorm_vec_kernel<TW, TO, NV_>, x, (const float*)y, (const TW*)w, \
-                                                   (TO*)copy, H, eps))))
+                                                   (TO*)copy, H, eps, (const TW*)next_w, (TO*)next_out, next_eps))))
         if (nv <= 1) ADDN_LAUNCH(1);
         else if (nv == 2) ADDN_LAUNCH(2);
         else ADDN_LAUNCH(4);
@@ -498,7 +528,7 @@ TQ_EXPORT int tq_add_rmsnorm(float* x, const void* y, int y_dtype, const void* w
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,
         (tq_launch(R, threads, 0, stream)(add_rmsnorm_kernel<TY, TW, TO>, x, (const TY*)y, (const TW*)w, (TO*)copy, H,
-                                          eps)))));
+                                          eps, (const TW*)next_w, (TO*)next_out, next_eps)))));
     TQ_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }
@@ -635,19 +665,22 @@ TQ_EXPORT int tq_glu_table_rows(const float* z, const int* tokens, const void* t
 }
 
 // ---------------------------------------------------------------------------------------
-// x[t, j] = x[t, j] * scale + bias[j] for j < N, rows of `stride` floats (bias may be null).
+// x[t, j] = x[t, j] * scale + bias[j] for j < N, rows of `stride` floats (bias may be null).  Grid (row, column chunks).
 // ---------------------------------------------------------------------------------------
 __global__ void scale_bias_cols_kernel(float* __restrict__ x, const float* __restrict__ bias, float scale, int N, int stride) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     float* row = x + (size_t)blockIdx.x * stride;
-    for (int j = threadIdx.x; j < N; j += blockDim.x) row[j] = bias ? row[j] * scale + bias[j] : row[j] * scale;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < N; j += gridDim.y * blockDim.x)
+        row[j] = bias ? row[j] * scale + bias[j] : row[j] * scale;
 }
 
 TQ_EXPORT int tq_scale_bias_cols(float* x, const float* bias, float scale, int T_, int N, int stride, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(N > 0 && N <= stride, "scale_bias_cols: %d columns of rows of %d", N, stride);
-    tq_launch(T_, N >= 1024 ? 256 : 128, 0, stream)(scale_bias_cols_kernel, x, bias, scale, N, stride);
+    // a few rows of many columns (a head's logits) spread over blocks by columns as well: 2048 columns a block
+    const int threads = N >= 1024 ? 256 : 128;
+    tq_launch(dim3(T_, (N + 8 * threads - 1) / (8 * threads)), threads, 0, stream)(scale_bias_cols_kernel, x, bias, scale, N, stride);
     TQ_CHECK_LAUNCH("scale_bias_cols");
     return 0;
 }

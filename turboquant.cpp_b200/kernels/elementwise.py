@@ -180,15 +180,23 @@ def embed_pair_rows(tokens: torch.Tensor, table: torch.Tensor, pair: Optional[to
 
 
 def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
-                copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+                copy: Optional[torch.Tensor] = None, next_weight: Optional[torch.Tensor] = None,
+                next_out: Optional[torch.Tensor] = None, next_eps: Optional[float] = None) -> torch.Tensor:
     """x += y / sqrt(mean(y^2) + eps) * weight, row by row in float32 (the norm sits on the sub-layer's output);
-    `copy` receives the new x in its own dtype."""
+    `copy` receives the new x in its own dtype.  next_weight, next_out: the norm that reads the new x next is taken
+    in the same pass, next_out = x / sqrt(mean(x^2) + next_eps) * next_weight (next_weight in weight's dtype,
+    next_out in copy's if both are given)."""
     want_f32(x, "the residual stream")
     R, H = x.shape
+    if next_out is not None:
+        if next_weight is None or next_weight.dtype != weight.dtype or (copy is not None and copy.dtype != next_out.dtype):
+            raise KernelError("add_rmsnorm: the following norm's weight and output must share the dtypes of weight and copy")
+    side = copy if copy is not None else next_out
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_add_rmsnorm(ptr(x), ptr(y), c_int(code(y.dtype)), ptr(weight), c_int(code(weight.dtype)),
-                                   ptr(copy), c_int(code(copy.dtype) if copy is not None else 0), c_int(R), c_int(H),
-                                   c_float(eps), stream()))
+                                   ptr(copy), c_int(code(side.dtype) if side is not None else 0), c_int(R), c_int(H),
+                                   c_float(eps), ptr(next_weight if next_out is not None else None), ptr(next_out),
+                                   c_float(eps if next_eps is None else next_eps), stream()))
     return x
 
 

@@ -60,6 +60,8 @@ class SisepelModel(DecoderModel):
                 after.append(TokenSideInput(p + "side.", SIDE_TABLE, cfg.vocab, cfg.side_dim * len(cfg.layers),
                                             i * cfg.side_dim, cfg.side_dim, W, cfg.eps))
             blocks.append(SandwichBlock(norm(p + "norm1"), mixer, norm(p + "norm1b"), ffn_norm, ffn, ffn_post, after))
+        for b, nxt in zip(blocks, blocks[1:]):               # the layers run in the listed order, each once
+            b.next_norm = nxt.mixer_norm
         super().__init__(cfg, dtype, embedding=Embedding("embed", cfg.vocab, W), blocks=blocks,
                          schedule=[ScheduleEntry(i) for i in range(len(blocks))],
                          final_norm=norm("final.norm"), head=LMHead("head", cfg.vocab, W, scale=cfg.logit_scale))

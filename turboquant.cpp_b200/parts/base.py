@@ -17,7 +17,7 @@ Interfaces
 ----------
 Part            weight_specs() -> [WeightSpec]; bind(store); kernels() -> names of kernel files
 Norm            forward(x, out_dtype, rows, add) -> xn; add_forward(x, y) -> xn (x += y in fp32, then the norm);
-                add_normed(x, y, copy) (x += norm(y))
+                add_normed(x, y, copy, then, then_dtype) (x += norm(y); the norm `then` of the sum along with it)
 PositionEncoding  tables() -> (cos, sin, pairing) or None; apply(q, k, positions)
 Mixer           cache_need() -> KVNeed | None; state_need() -> StateNeed | None; capturable() -> bool;
                 forward(xn, ctx, cache) -> y [T, hidden]
@@ -129,9 +129,11 @@ class Norm(Part):
     def add_forward(self, x: torch.Tensor, y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         raise NotImplementedError
 
-    def add_normed(self, x: torch.Tensor, y: torch.Tensor, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def add_normed(self, x: torch.Tensor, y: torch.Tensor, copy: Optional[torch.Tensor] = None, then: Optional["Norm"] = None,
+                   then_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
         """x += norm(y) in fp32, for blocks whose norms sit on the sub-layers' outputs; `copy` receives the new x
-        in its own dtype."""
+        in its own dtype.  then: the norm that reads the new x next; where this norm can take it in the same pass
+        it returns that norm's output in then_dtype, else None (without `then`: x)."""
         raise NotImplementedError
 
 

@@ -108,10 +108,14 @@ class PostNormBlock(Block):
         return x, None
 
 
+NORMED_STREAM = "normed_stream"       # StepContext.carry: the stream under the next block's first norm
+
+
 class SandwichBlock(Block):
     """x += post_norm(mixer(pre_norm(x))); x += post_norm(feed_forward(pre_norm(x))): a norm before and one after each
     sub-layer.  The feed-forward (with its two norms) may be absent.  `after`: parts that change the stream once
-    the sub-layers have run (`apply(x, ctx)`, e.g. a per-layer token input).  The stream stays float32."""
+    the sub-layers have run (`apply(x, ctx, cast, then)`, e.g. a per-layer token input).  The stream stays float32.
+    `next_norm` (set by a model whose blocks run in a fixed order): the norm the next block starts with."""
 
     def __init__(self, mixer_norm: Norm, mixer: Mixer, mixer_post: Norm, ffn_norm: Optional[Norm] = None,
                  ffn: Optional[FeedForward] = None, ffn_post: Optional[Norm] = None, after=()):
@@ -120,6 +124,7 @@ class SandwichBlock(Block):
         self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
         self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
         self.after = list(after)
+        self.next_norm: Optional[Norm] = None        # the first norm of the block that runs next, if the model names it
 
     def parts(self):
         own = [self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post] + self.after
@@ -153,16 +158,40 @@ class SandwichBlock(Block):
     def kernels(self) -> List[str]:
         return ["elementwise"] + [k for p in self._direct() for k in p.kernels()]
 
+    @staticmethod
+    def _add(norm: Norm, x, y, ctx, copy=None, then: Optional[Norm] = None):
+        """x += norm(y); returns the norm `then` of the new x where it could be taken in the same pass, else None."""
+        if then is None or not hasattr(norm, "weight"):
+            norm.add_normed(x, y, copy)
+            return None
+        return norm.add_normed(x, y, copy, then=then, then_dtype=ctx.act_dtype)
+
     def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        if pending is None:
-            xn = self.mixer_norm.forward(x, ctx.act_dtype)
-        else:                                        # a block of another kind ran before and left its sum open
+        # the block before may have taken this block's first norm along with its last sum (`next_norm`)
+        xn = ctx.carry.pop(NORMED_STREAM, None) if ctx.carry is not None else None
+        if pending is not None:                      # a block of another kind ran before and left its sum open
             xn = self.mixer_norm.add_forward(x, pending, ctx.act_dtype)
-        self.mixer_post.add_normed(x, self.mixer.forward(xn, ctx, cache))
+        elif xn is None:
+            xn = self.mixer_norm.forward(x, ctx.act_dtype)
+        # every sum into the stream takes the norm that reads the stream next along: the feed-forward's, or, from
+        # the block's last sum, the next block's first; the parts after the sub-layers get the stream in the
+        # activation dtype from the sum before them
+        exact = ctx.act_dtype == torch.float32
+        n_after = len(self.after)
+        cast = lambda wanted: torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device) if wanted and not exact else None
+        out_norm = self.next_norm if ctx.carry is not None else None
+        last = self.ffn is None and not n_after
+        h = cast(self.ffn is None and n_after)
+        xn = self._add(self.mixer_post, x, self.mixer.forward(xn, ctx, cache), ctx, copy=h,
+                       then=self.ffn_norm if self.ffn is not None else (out_norm if last else None))
         if self.ffn is not None:
-            xn = self.ffn_norm.forward(x, ctx.act_dtype)
-            self.ffn_post.add_normed(x, self.ffn.forward(xn, ctx))
-        for part in self.after:
-            part.apply(x, ctx)
+            if xn is None:
+                xn = self.ffn_norm.forward(x, ctx.act_dtype)
+            h = cast(n_after)
+            xn = self._add(self.ffn_post, x, self.ffn.forward(xn, ctx), ctx, copy=h, then=None if n_after else out_norm)
+        for k, part in enumerate(self.after):
+            xn = part.apply(x, ctx, cast=h if k == 0 else None, then=out_norm if k == n_after - 1 else None)
+        if xn is not None and out_norm is not None:
+            ctx.carry[NORMED_STREAM] = xn
         return x, None

@@ -40,8 +40,16 @@ class RMSNorm(Norm):
         out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
         return K.rmsnorm(x, self.weight, self.eps, out, add=y)
 
-    def add_normed(self, x, y, copy=None):
-        return K.add_rmsnorm(x, y, self.weight, self.eps, copy)
+    def add_normed(self, x, y, copy=None, then=None, then_dtype=None):
+        """x += norm(y).  then (an RMSNorm of the same weight dtype): its norm of the new x is taken in the same pass
+        and returned in then_dtype (None where the two weights' dtypes differ: the caller runs it by itself)."""
+        if then is not None and isinstance(then, RMSNorm) and then.weight.dtype == self.weight.dtype and \
+                (copy is None or copy.dtype == then_dtype):
+            out = torch.empty((x.shape[0], self.size), dtype=then_dtype, device=x.device)
+            K.add_rmsnorm(x, y, self.weight, self.eps, copy, then.weight, out, then.eps)
+            return out
+        K.add_rmsnorm(x, y, self.weight, self.eps, copy)
+        return None if then is not None else x
 
 
 register_norm("rmsnorm", RMSNorm)

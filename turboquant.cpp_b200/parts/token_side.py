@@ -11,7 +11,7 @@ sum into the stream are float32.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -48,13 +48,21 @@ class TokenSideInput(Part):
         wb = lambda w: 0 if w is None else w.numel() * w.element_size()
         return {"matmul": (wb(self.w_gate) + wb(self.w_proj), 4.0 * n_tokens * self.hidden * self.dim)}
 
-    def apply(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        """x (float32 [T, hidden], the residual stream) is changed in place."""
+    def apply(self, x: torch.Tensor, ctx: StepContext, cast: Optional[torch.Tensor] = None, then=None):
+        """x (float32 [T, hidden], the residual stream) is changed in place.  cast: x in the activation dtype, where
+        the caller has it; then: a norm (weight, eps) that reads the new x next, taken in the same pass and returned
+        (None where it was not)."""
         T, dev = x.shape[0], x.device
         exact = ctx.act_dtype == torch.float32
-        h = x if exact else K.map_elements(x, torch.empty(x.shape, dtype=ctx.act_dtype, device=dev))
+        h = x if exact else (cast if cast is not None else K.map_elements(x, torch.empty(x.shape, dtype=ctx.act_dtype, device=dev)))
         z = linear(h, self.w_gate, out_dtype=torch.float32)
         g = torch.empty((T, self.dim), dtype=ctx.act_dtype, device=dev)
         K.glu_table_rows(z, ctx.tokens, self.table, self.col0, g, self.glu)
         y = linear(g, self.w_proj, out_dtype=torch.float32)
-        return K.add_rmsnorm(x, y, self.w_norm, self.eps)
+        w = getattr(then, "weight", None)
+        if w is not None and w.dtype == self.w_norm.dtype:
+            out = torch.empty(x.shape, dtype=ctx.act_dtype, device=dev)
+            K.add_rmsnorm(x, y, self.w_norm, self.eps, None, w, out, then.eps)
+            return out
+        K.add_rmsnorm(x, y, self.w_norm, self.eps)
+        return None
