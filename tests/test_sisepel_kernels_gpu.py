@@ -294,6 +294,27 @@ def test_a_sum_under_a_norm_with_the_next_norm_along(R, H, wdtype, odtype):
     assert torch.equal(xd2, xd) and rel(nxt2, P.norm(want, host(wn), 1e-5)) < tol
 
 
+@pytest.mark.parametrize("R,H", [(1, 36), (3, 256), (7, 1000), (2, 2048), (2, 5000), (5, 37)])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_two_normed_branches_under_the_sum_and_the_next_norm(R, H, wdtype, odtype):
+    """x += norm(mean of two normed branches) and the next norm of x in one pass, both row forms of the kernel; the
+    branches differ in size by orders of magnitude, so a shared norm or a missing one would show."""
+    from turboquant_cpp_b200.kernels import elementwise as KE
+    rng = np.random.default_rng(R * H + 1)
+    x = host(dev(rng.standard_normal((R, H))))
+    a, b = host(dev(40.0 * rng.standard_normal((R, H)))), host(dev(0.003 * rng.standard_normal((R, H))))
+    wa, wb, w, wn = (dev(1 + 0.3 * rng.standard_normal(H), wdtype) for _ in range(4))
+    m = 0.5 * (P.norm(a, host(wa), 2e-5) + P.norm(b, host(wb), 2e-5))
+    want = x + P.norm(m, host(w), 1e-4)
+    tol = 1e-5 if odtype == torch.float32 else 5e-3
+    xd, copy, nxt = dev(x), torch.empty((R, H), dtype=odtype, device=DEV), torch.empty((R, H), dtype=odtype, device=DEV)
+    KE.add_rmsnorm_pair(xd, dev(a), wa, dev(b), wb, 2e-5, w, 1e-4, copy, wn, nxt, 3e-4)
+    assert rel(xd, want) < 1e-5 and rel(copy, want) < tol and rel(nxt, P.norm(want, host(wn), 3e-4)) < tol
+    xd2 = dev(x)
+    KE.add_rmsnorm_pair(xd2, dev(a), wa, dev(b), wb, 2e-5, w, 1e-4)      # the sum alone
+    assert torch.equal(xd2, xd)
+
+
 @pytest.mark.parametrize("T,D,col0,width", [(1, 24, 0, 24), (9, 6, 12, 30), (40, 1, 3, 4), (5, 130, 130, 390)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gated_slice_of_a_token_table(T, D, col0, width, dtype):

@@ -635,6 +635,167 @@ TQ_EXPORT int tq_mean_of_norms(const float* a, const void* wa, const float* b, c
 }
 
 // ---------------------------------------------------------------------------------------
+// The mean of two normed branches under a further norm, summed into the stream, with the norm that reads the stream
+// next (optional) in the same pass:
+//   m[r] = (a[r] / sqrt(mean(a[r]^2) + pair_eps) * wa + b[r] / sqrt(mean(b[r]^2) + pair_eps) * wb) / 2
+//   x[r] += m[r] / sqrt(mean(m[r]^2) + eps) * w;   next_out[r] = x[r] / sqrt(mean(x[r]^2) + next_eps) * next_w
+// all in fp32.  The vector form keeps a thread's float4 pieces of the row in registers from the first sums to the last
+// output (rows of a multiple of four, up to 4 * ADDN_THREADS * NV elements); the plain form reads the row again.
+// ---------------------------------------------------------------------------------------
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(ADDN_THREADS)
+add_rmsnorm_pair_vec_kernel(float* __restrict__ x, const float* __restrict__ a, const TW* __restrict__ wa,
+                            const float* __restrict__ b, const TW* __restrict__ wb, float pair_eps,
+                            const TW* __restrict__ w, TO* __restrict__ copy, int H, float eps,
+                            const TW* __restrict__ next_w, TO* __restrict__ next_out, float next_eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const float4* ar = reinterpret_cast<const float4*>(a + r * H);
+    const float4* br = reinterpret_cast<const float4*>(b + r * H);
+    float4* xr = reinterpret_cast<float4*>(x + r * H);
+    const int n4 = H / 4;
+    float4 av[NV], bv[NV], xv[NV];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        av[k] = bv[k] = xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            av[k] = ar[i];
+            bv[k] = br[i];
+            xv[k] = xr[i];
+        }
+        sa += av[k].x * av[k].x + av[k].y * av[k].y + av[k].z * av[k].z + av[k].w * av[k].w;
+        sb += bv[k].x * bv[k].x + bv[k].y * bv[k].y + bv[k].z * bv[k].z + bv[k].w * bv[k].w;
+    }
+    sa = tq_block_sum(sa, scratch);
+    sb = tq_block_sum(sb, scratch);
+    const float ra = 1.0f / sqrtf(sa / (float)H + pair_eps), rb = 1.0f / sqrtf(sb / (float)H + pair_eps);
+    float sm = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        if (i < n4) {
+            float4 m;
+            m.x = 0.5f * (av[k].x * ra * tq_to_float(wa[4 * i]) + bv[k].x * rb * tq_to_float(wb[4 * i]));
+            m.y = 0.5f * (av[k].y * ra * tq_to_float(wa[4 * i + 1]) + bv[k].y * rb * tq_to_float(wb[4 * i + 1]));
+            m.z = 0.5f * (av[k].z * ra * tq_to_float(wa[4 * i + 2]) + bv[k].z * rb * tq_to_float(wb[4 * i + 2]));
+            m.w = 0.5f * (av[k].w * ra * tq_to_float(wa[4 * i + 3]) + bv[k].w * rb * tq_to_float(wb[4 * i + 3]));
+            av[k] = m;
+            sm += m.x * m.x + m.y * m.y + m.z * m.z + m.w * m.w;
+        }
+    }
+    sm = tq_block_sum(sm, scratch);
+    const float rs = 1.0f / sqrtf(sm / (float)H + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        if (i < n4) {
+            float4 v;
+            v.x = xv[k].x + av[k].x * rs * tq_to_float(w[4 * i]);
+            v.y = xv[k].y + av[k].y * rs * tq_to_float(w[4 * i + 1]);
+            v.z = xv[k].z + av[k].z * rs * tq_to_float(w[4 * i + 2]);
+            v.w = xv[k].w + av[k].w * rs * tq_to_float(w[4 * i + 3]);
+            xr[i] = v;
+            xv[k] = v;
+            s2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            if (copy) {
+                TO* c = copy + r * H + 4 * i;
+                c[0] = tq_from_float<TO>(v.x); c[1] = tq_from_float<TO>(v.y);
+                c[2] = tq_from_float<TO>(v.z); c[3] = tq_from_float<TO>(v.w);
+            }
+        }
+    }
+    if (next_out == nullptr) return;               // the same for the whole block
+    s2 = tq_block_sum(s2, scratch);
+    const float rs2 = 1.0f / sqrtf(s2 / (float)H + next_eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        if (i < n4) {
+            TO* c = next_out + r * H + 4 * i;
+            c[0] = tq_from_float<TO>(xv[k].x * rs2 * tq_to_float(next_w[4 * i]));
+            c[1] = tq_from_float<TO>(xv[k].y * rs2 * tq_to_float(next_w[4 * i + 1]));
+            c[2] = tq_from_float<TO>(xv[k].z * rs2 * tq_to_float(next_w[4 * i + 2]));
+            c[3] = tq_from_float<TO>(xv[k].w * rs2 * tq_to_float(next_w[4 * i + 3]));
+        }
+    }
+}
+
+template <typename TW, typename TO>
+__global__ void add_rmsnorm_pair_kernel(float* __restrict__ x, const float* __restrict__ a, const TW* __restrict__ wa,
+                                        const float* __restrict__ b, const TW* __restrict__ wb, float pair_eps,
+                                        const TW* __restrict__ w, TO* __restrict__ copy, int H, float eps,
+                                        const TW* __restrict__ next_w, TO* __restrict__ next_out, float next_eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const float* ar = a + r * H;
+    const float* br = b + r * H;
+    float* xr = x + r * H;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        sa += ar[i] * ar[i];
+        sb += br[i] * br[i];
+    }
+    sa = tq_block_sum(sa, scratch);
+    sb = tq_block_sum(sb, scratch);
+    const float ra = 1.0f / sqrtf(sa / (float)H + pair_eps), rb = 1.0f / sqrtf(sb / (float)H + pair_eps);
+    auto mean = [&](int i) { return 0.5f * (ar[i] * ra * tq_to_float(wa[i]) + br[i] * rb * tq_to_float(wb[i])); };
+    float sm = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float m = mean(i);
+        sm += m * m;
+    }
+    sm = tq_block_sum(sm, scratch);
+    const float rs = 1.0f / sqrtf(sm / (float)H + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i] + mean(i) * rs * tq_to_float(w[i]);
+        xr[i] = v;
+        s2 += v * v;
+        if (copy) copy[r * H + i] = tq_from_float<TO>(v);
+    }
+    if (next_out == nullptr) return;               // the same for the whole block
+    s2 = tq_block_sum(s2, scratch);
+    const float rs2 = 1.0f / sqrtf(s2 / (float)H + next_eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)      // a thread reads back what it wrote itself
+        next_out[r * H + i] = tq_from_float<TO>(xr[i] * rs2 * tq_to_float(next_w[i]));
+}
+
+// wa, wb, w and next_w share one dtype; copy and next_out another.
+TQ_EXPORT int tq_add_rmsnorm_pair(float* x, const float* a, const void* wa, const float* b, const void* wb, float pair_eps,
+                                  const void* w, int w_dtype, void* copy, int copy_dtype, int R, int H, float eps,
+                                  const void* next_w, void* next_out, float next_eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(R > 0 && H > 0, "add_rmsnorm_pair: bad sizes R=%d H=%d", R, H);
+    TQ_REQUIRE(next_out == nullptr || next_w != nullptr, "add_rmsnorm_pair: a following norm without its weight%s", "");
+    if (H % 4 == 0 && H <= 4 * ADDN_THREADS * 4 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0) {
+        const int nv = (H / 4 + ADDN_THREADS - 1) / ADDN_THREADS;
+#define ADDP_LAUNCH(NV_)                                                                                           \
+        TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,                                                       \
+            (tq_launch(R, ADDN_THREADS, 0, stream)(add_rmsnorm_pair_vec_kernel<TW, TO, NV_>, x, a, (const TW*)wa, b, \
+                (const TW*)wb, pair_eps, (const TW*)w, (TO*)copy, H, eps, (const TW*)next_w, (TO*)next_out, next_eps))))
+        if (nv <= 1) ADDP_LAUNCH(1);
+        else if (nv == 2) ADDP_LAUNCH(2);
+        else ADDP_LAUNCH(4);
+#undef ADDP_LAUNCH
+        TQ_CHECK_LAUNCH("add_rmsnorm_pair");
+        return 0;
+    }
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,
+        (tq_launch(R, threads, 0, stream)(add_rmsnorm_pair_kernel<TW, TO>, x, a, (const TW*)wa, b, (const TW*)wb, pair_eps,
+                                          (const TW*)w, (TO*)copy, H, eps, (const TW*)next_w, (TO*)next_out, next_eps))));
+    TQ_CHECK_LAUNCH("add_rmsnorm_pair");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // A gated activation against rows of a table: out[t, j] = glu(z[t, j], table[tokens[t]][col0 + j]) for j < D
 // (z fp32 [T, D]; the table's rows have `stride` elements).
 // ---------------------------------------------------------------------------------------

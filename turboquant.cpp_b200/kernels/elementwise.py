@@ -200,6 +200,33 @@ def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     return x
 
 
+def add_rmsnorm_pair(x: torch.Tensor, a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, pair_eps: float,
+                     weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor] = None,
+                     next_weight: Optional[torch.Tensor] = None, next_out: Optional[torch.Tensor] = None,
+                     next_eps: Optional[float] = None) -> torch.Tensor:
+    """`mean_of_norms(a, wa, b, wb, pair_eps)` under `add_rmsnorm(x, ., weight, eps, copy, next...)` in one pass:
+    x += m / sqrt(mean(m^2) + eps) * weight with m the mean of the two normed branches.  a, b float32 [R, H]; the four
+    weights share a dtype."""
+    want_f32(x, "the residual stream")
+    want_f32(a, "the first branch")
+    want_f32(b, "the second branch")
+    R, H = x.shape
+    if a.shape != x.shape or b.shape != x.shape:
+        raise KernelError("add_rmsnorm_pair: the branches and the stream must agree in shape")
+    ws = [wa, wb, weight] + ([next_weight] if next_out is not None else [])
+    if any(w is None or w.dtype != weight.dtype for w in ws):
+        raise KernelError("add_rmsnorm_pair: the norms' weights must share a dtype")
+    if next_out is not None and copy is not None and copy.dtype != next_out.dtype:
+        raise KernelError("add_rmsnorm_pair: copy and the following norm's output must share a dtype")
+    side = copy if copy is not None else next_out
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_add_rmsnorm_pair(ptr(x), ptr(a), ptr(wa), ptr(b), ptr(wb), c_float(pair_eps), ptr(weight),
+                                        c_int(code(weight.dtype)), ptr(copy), c_int(code(side.dtype) if side is not None else 0),
+                                        c_int(R), c_int(H), c_float(eps), ptr(next_weight if next_out is not None else None),
+                                        ptr(next_out), c_float(eps if next_eps is None else next_eps), stream()))
+    return x
+
+
 MAP_COPY, MAP_RELU_SQUARED = 0, 1
 
 

@@ -10,6 +10,7 @@ from typing import List, Optional, Tuple
 
 import torch
 
+from ..kernels import elementwise as K
 from ..weights.loader import WeightSpec, WeightStore
 from .base import Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, StateNeed, StepContext
 
@@ -183,8 +184,17 @@ class SandwichBlock(Block):
         out_norm = self.next_norm if ctx.carry is not None else None
         last = self.ffn is None and not n_after
         h = cast(self.ffn is None and n_after)
-        xn = self._add(self.mixer_post, x, self.mixer.forward(xn, ctx, cache), ctx, copy=h,
-                       then=self.ffn_norm if self.ffn is not None else (out_norm if last else None))
+        then = self.ffn_norm if self.ffn is not None else (out_norm if last else None)
+        done = False
+        if hasattr(self.mixer, "forward_branches") and hasattr(self.mixer_post, "add_normed_pair"):
+            # a mixer of two normed branches: their norms and mean run inside the sum's pass
+            pair = self.mixer.forward_branches(xn, ctx, cache)
+            done, xn = self.mixer_post.add_normed_pair(x, pair, h, then=then, then_dtype=ctx.act_dtype)
+            if not done:
+                a, wa, b, wb, eps = pair
+                xn = self._add(self.mixer_post, x, K.mean_of_norms(a, wa, b, wb, eps, torch.empty_like(a)), ctx, copy=h, then=then)
+        else:
+            xn = self._add(self.mixer_post, x, self.mixer.forward(xn, ctx, cache), ctx, copy=h, then=then)
         if self.ffn is not None:
             if xn is None:
                 xn = self.ffn_norm.forward(x, ctx.act_dtype)

@@ -52,4 +52,19 @@ class RMSNorm(Norm):
         return None if then is not None else x
 
 
+    def add_normed_pair(self, x, pair, copy=None, then=None, then_dtype=None):
+        """x += norm(mean of two normed branches); pair = (a, wa, b, wb, eps) as a mixer of two branches leaves them
+        (`forward_branches`).  Returns (done, normed): done False where the weights' dtypes differ and nothing was
+        computed; normed: the norm `then` of the new x where it was taken along, else None."""
+        a, wa, b, wb, pair_eps = pair
+        if wa.dtype != self.weight.dtype or wb.dtype != self.weight.dtype:
+            return False, None
+        if then is not None and isinstance(then, RMSNorm) and then.weight.dtype == self.weight.dtype and \
+                (copy is None or copy.dtype == then_dtype):
+            out = torch.empty((x.shape[0], self.size), dtype=then_dtype, device=x.device)
+            K.add_rmsnorm_pair(x, a, wa, b, wb, pair_eps, self.weight, self.eps, copy, then.weight, out, then.eps)
+            return True, out
+        K.add_rmsnorm_pair(x, a, wa, b, wb, pair_eps, self.weight, self.eps, copy)
+        return True, None
+
 register_norm("rmsnorm", RMSNorm)

@@ -66,7 +66,9 @@ class ParallelMixer(Mixer):
     def step_work(self, n_tokens, kv_tokens):
         return {}                # the branches are listed among the block's parts and say what they do themselves
 
-    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+    def forward_branches(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache):
+        """The two branches' outputs before their norms, (a, w_left, b, w_right, eps), for a block whose norm on the
+        mixer's output takes the branches' norms and their mean in its own pass."""
         if self.w_in is not None:
             proj = linear(xn, self.w_in, out_dtype=torch.float32)
             a = self.left.forward(xn, ctx, cache, projected=proj)
@@ -74,8 +76,12 @@ class ParallelMixer(Mixer):
         else:
             a = self.left.forward(xn, ctx, cache)
             b = self.right.forward(xn, ctx, cache)
+        return a, self.w_left, b, self.w_right, self.eps
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        a, wa, b, wb, eps = self.forward_branches(xn, ctx, cache)
         out = torch.empty((xn.shape[0], self.hidden), dtype=torch.float32, device=xn.device)
-        return K.mean_of_norms(a, self.w_left, b, self.w_right, self.eps, out)
+        return K.mean_of_norms(a, wa, b, wb, eps, out)
 
 
 register_mixer("parallel", ParallelMixer)
