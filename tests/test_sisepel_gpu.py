@@ -102,6 +102,49 @@ def test_prompts_in_portions(folders, name, sizes, dtype):
         eng.release()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,sizes", [("a", [700]), ("b", [333, 130, 237]), ("c", [129, 571])])
+def test_long_prompts_whose_recurrence_runs_in_chunks(folders, name, sizes, dtype, monkeypatch):
+    """Runs long enough for the retention mixer to cut them into chunks that it scans side by side (whole, and in
+    portions that go on from a kept state), beside a short request.  float32: against the plain model.  bfloat16:
+    against the same engine with the cutting switched off, position by position (among 700 positions some enlarge a
+    rounding beyond any bound that would still tell a fault; both paths round alike, so they stay together)."""
+    from turboquant_cpp_b200.parts.retention import RetentionMixer
+    cfg, folder = CONFIGS[name], folders[name]
+    toks, other = tokens_for(cfg, sum(sizes), 21), tokens_for(cfg, len(sizes) + 40, 22)
+    steps, at = [], 0
+    for i, n in enumerate(sizes):
+        step = [("p", toks[at:at + n], list(range(n)))]
+        step.append(("o", other[:41], list(range(41))) if i == 0 else ("o", [other[40 + i]], [0]))
+        steps.append(step)
+        at += n
+
+    def run():
+        eng = engine_for(folder, dtype, max_tokens=1024)
+        try:
+            return run_steps_with_routing(eng, steps, {len(steps) - 1: ["p", "o"]})
+        finally:
+            eng.release()
+
+    cut = []
+    plan = RetentionMixer._chunks
+    monkeypatch.setattr(RetentionMixer, "_chunks", lambda self, ctx: cut.append(plan(self, ctx)) or cut[-1])
+    got, routing = run()
+    assert any(c is not None for c in cut)                    # the runs were cut
+    if dtype == "float32":
+        check_against_plain(plain_model(folder), toks, got["p"], routing["p"], dtype, f"{name} long prompt")
+        check_against_plain(plain_model(folder), other, got["o"], routing["o"], dtype, f"{name} beside a long prompt")
+        return
+    monkeypatch.setattr(RetentionMixer, "_chunks", lambda self, ctx: None)
+    whole, _ = run()
+    for rid in ("p", "o"):
+        ref = np.stack([whole[rid][p] for p in sorted(whole[rid])])
+        rows = np.stack([got[rid][p] for p in sorted(whole[rid])])
+        d = rows - ref
+        e = np.sqrt((d * d).mean(axis=1)) / ref.std()
+        assert e.max() < 2e-2, f"{name} {rid}: position {int(e.argmax())} differs by {e.max():.3e} between the cut and the whole recurrence"
+
+
 def test_slots_and_pages_used_again_carry_nothing_over(folders):
     """A request run after others have ended gets their slot (its retention state) and pages; its logits are those of
     a fresh engine."""

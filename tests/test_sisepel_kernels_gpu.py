@@ -219,6 +219,62 @@ def test_retention_over_portions_in_used_slots(case):
     assert float(state[0].min()) == 7.0 and float(state[4].max()) == 7.0       # other slots are not touched
 
 
+@pytest.mark.parametrize("case", RET_CASES)
+def test_retention_in_chunks_side_by_side(case):
+    """Long runs cut into chunks that are scanned side by side from zero states, put right by the states they should
+    have started from, and scanned again: the outputs of the plain recurrence, over two portions (the second goes
+    on from kept states), with chunks of unequal sizes, a last chunk of one token, and other slots left alone."""
+    from turboquant_cpp_b200.kernels import ssm as KS
+    heads, dk, dv, decay, rot = case
+    rng = np.random.default_rng(heads * 10 + dv)
+    lens = {0: 341, 1: 150}
+    m = {"decay": list(decay), "rot": rot, "heads": heads, "dim": dk, "vdim": dv}
+    qk, inner = heads * dk, heads * dv
+    proj = {s: host(dev(rng.standard_normal((n, 2 * qk + inner)))) for s, n in lens.items()}
+    want, last = {}, {}
+    for s, n in lens.items():
+        pr = proj[s]
+        o, last[s] = P.retention_core(pr[:, :qk].reshape(n, heads, dk), pr[:, qk:2 * qk].reshape(n, heads, dk),
+                                      pr[:, 2 * qk:].reshape(n, heads, dv), m)
+        want[s] = o.reshape(n, inner)
+    state = torch.full((4, heads, dv, dk), 7.0, dtype=torch.float32, device=DEV)
+    slots = {0: 2, 1: 0}
+    for s in slots.values():
+        state[s].zero_()
+    decay_dev = dev(np.array(decay))
+    at = {0: 0, 1: 0}
+    for (n0, n1), size in (((193, 100), 48), ((148, 50), 64)):
+        pr = dev(np.concatenate([proj[0][at[0]:at[0] + n0], proj[1][at[1]:at[1] + n1]]))
+        T = n0 + n1
+        positions = i32(list(range(at[0], at[0] + n0)) + list(range(at[1], at[1] + n1)))
+        xbc = torch.empty((T, inner + 2 * qk), dtype=torch.float32, device=DEV)
+        KS.retention_prepare(pr, 0, qk, 2 * qk, xbc, frequencies(rot), rot["dims"] if rot else 0, True, dk ** -0.5, positions,
+                             heads, dk, dv)
+        cu, seq_chunks, lo = [0], [0], 0
+        for n in (n0, n1):
+            cu += [lo + min(n, c + size) for c in range(0, n, size)]
+            seq_chunks.append(len(cu) - 1)
+            lo += n
+        n_chunks = len(cu) - 1
+        ends = torch.zeros((n_chunks, heads, dv, dk), dtype=torch.float32, device=DEV)
+        starts = torch.full((n_chunks, heads, dv, dk), 3.0, dtype=torch.float32, device=DEV)
+        y = torch.full((T, inner), float("nan"), dtype=torch.float32, device=DEV)
+        ids = i32(list(range(n_chunks)))
+        KS.ssm_scan(xbc, None, 0, None, None, None, ends, None, heads, dv, dk, heads, i32(cu), ids, fixed_decay=decay_dev)   # the states alone
+        KS.retention_combine(state, i32([slots[0], slots[1]]), ends, starts, i32(seq_chunks), i32(cu), decay_dev)
+        KS.ssm_scan(xbc, None, 0, None, None, None, starts, y, heads, dv, dk, heads, i32(cu), ids, fixed_decay=decay_dev)
+        for s, lo, n in ((0, 0, n0), (1, n0, n1)):
+            ref = want[s][at[s]:at[s] + n]
+            assert np.abs(host(y[lo:lo + n]) - ref).max() < 3e-5 * max(1.0, np.abs(want[s]).max()), (s, at[s], n)
+        at[0] += n0
+        at[1] += n1
+    assert at == lens
+    for s in lens:                                            # the kept state is the plain recurrence's, [heads, dk, dv] there
+        kept = host(state[slots[s]]).transpose(0, 2, 1)
+        assert np.abs(kept - last[s]).max() < 3e-5 * max(1.0, np.abs(last[s]).max())
+    assert float(state[1].min()) == 7.0 and float(state[3].max()) == 7.0
+
+
 def test_a_far_token_speaks_through_a_head_that_forgets_nothing():
     """A key along one direction at position 3, a query along it 900 tokens later, a decay of one: the output holds that
     token's value at full weight; the head beside it, with a decay of 0.9, has lost it."""

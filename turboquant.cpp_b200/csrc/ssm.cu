@@ -124,7 +124,8 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
 #define SSM_COLS 32           // columns of the state per block
 
 // SSM_CPW columns per warp (4 or 2), SSM_COLS / SSM_CPW warps, 32 / SSM_CPW steps whose sums are taken together
-template <typename TW, int RPL, int TC, int SSM_CPW>
+// OUT false: the state is walked on and no output written (y is not touched)
+template <typename TW, int RPL, int TC, int SSM_CPW, bool OUT>
 __global__ void __launch_bounds__(32 * SSM_COLS / SSM_CPW)
 ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
@@ -229,7 +230,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
 #pragma unroll
                             for (int c = 0; c < SSM_CPW; ++c) {
                                 S[r][c] = a * S[r][c] + bv * xv[c];
-                                v[j * SSM_CPW + c] += S[r][c] * cv;
+                                if constexpr (OUT) v[j * SSM_CPW + c] += S[r][c] * cv;
                             }
                         }
                     }
@@ -237,6 +238,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
             };
             if (t8 + SSM_GROUP <= tc) steps(std::true_type{});
             else steps(std::false_type{});
+            if constexpr (!OUT) continue;
             // 32 sums over 32 lanes: every round a lane keeps the half of its values that its bit names and gets
             // the other lane's share of that half, so after five rounds lane l holds the whole sum number l
 #pragma unroll
@@ -265,16 +267,27 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
     }
 }
 
-#define SSM_LAUNCH(RPL_, TC_, CPW_)                                                                               \
+#define SSM_LAUNCH_OUT(RPL_, TC_, CPW_, OUT_)                                                                      \
     TQ_DISPATCH(w_dtype, TW,                                                                                      \
-        (tq_launch(grid, 32 * SSM_COLS / CPW_, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_, CPW_>, xbc, C, proj, P, dt_off, \
+        (tq_launch(grid, 32 * SSM_COLS / CPW_, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_, CPW_, OUT_>, xbc, C, proj, P, dt_off, \
             (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, \
             cu_seqlens, slots, fixed_decay)))
+#define SSM_LAUNCH(RPL_, TC_, CPW_)                                                                               \
+    do {                                                                                                          \
+        if (y == nullptr) SSM_LAUNCH_OUT(RPL_, TC_, CPW_, false);                                                 \
+        else SSM_LAUNCH_OUT(RPL_, TC_, CPW_, true);                                                               \
+    } while (0)
 
 // TQ_SSM_CPW=2: sixteen warps of two columns instead of eight of four (measured slower at every size tried)
 static int ssm_cpw() {
     static const int v = [] { const char* e = getenv("TQ_SSM_CPW"); return e && e[0] == '2' ? 2 : 4; }();
     return v;
+}
+
+// Warps a launch makes (a warp owns SSM_CPW columns of a head's state): callers that may cut long runs into chunks
+// weigh them against the warps the GPU holds.
+TQ_EXPORT int tq_ssm_scan_warps(int n_seqs, int heads, int vdim) {
+    return n_seqs * heads * ((vdim + SSM_COLS - 1) / SSM_COLS) * (SSM_COLS / ssm_cpw());
 }
 
 TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
@@ -472,5 +485,44 @@ TQ_EXPORT int tq_retention_prepare(const float* proj, int P, int q_off, int k_of
     tq_launch(dim3(T_, (2 * heads + 3) / 4), 128, 0, stream)(retention_prepare_kernel, proj, P, q_off, k_off, v_off, out, freq, rot_dims, halves, k_scale,
                                   positions, heads, dk, dv);
     TQ_CHECK_LAUNCH("retention_prepare");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// retention_combine: a long run cut into chunks that were scanned side by side, each from a zero state.  With
+// ends[c] the state a chunk reached by itself and len_c its tokens, the state the chunk should have started from is
+//   start[c0] = the sequence's kept state;  start[c + 1] = decay_h^len_c * start[c] + ends[c]
+// (the recurrence is linear in the state), and the last of these is the sequence's new kept state.  One thread per
+// element of a sequence's state walks the sequence's chunks; grid (elements / 256, sequences).  A second scan of the
+// chunks from starts[] then gives the outputs.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+retention_combine_kernel(float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
+                         const float* __restrict__ ends, float* __restrict__ starts, const int* __restrict__ seq_chunks,
+                         const int* __restrict__ cu_chunks, const float* __restrict__ decay, int per_head, int n_elems) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_elems) return;
+    const int s = blockIdx.y;
+    const float d = decay[e / per_head];
+    float* cell = state + (size_t)slots[s] * slot_stride + e;
+    float S = *cell;
+    for (int c = seq_chunks[s]; c < seq_chunks[s + 1]; ++c) {
+        starts[(size_t)c * n_elems + e] = S;
+        S = powf(d, (float)(cu_chunks[c + 1] - cu_chunks[c])) * S + ends[(size_t)c * n_elems + e];
+    }
+    *cell = S;
+}
+
+TQ_EXPORT int tq_retention_combine(float* state, long long slot_stride, const int* slots, const float* ends, float* starts,
+                                   const int* seq_chunks, const int* cu_chunks, const float* decay, int n_seqs, int heads,
+                                   int per_head, cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && per_head >= 1 && n_seqs <= 65535, "retention_combine: %d heads of %d in %d sequences", heads, per_head, n_seqs);
+    const int n_elems = heads * per_head;
+    tq_launch(dim3((n_elems + 255) / 256, n_seqs), 256, 0, stream)(retention_combine_kernel, state, slot_stride, slots, ends,
+                                                                  starts, seq_chunks, cu_chunks, decay, per_head, n_elems);
+    TQ_CHECK_LAUNCH("retention_combine");
     return 0;
 }

@@ -36,15 +36,16 @@ def conv_silu(proj: torch.Tensor, off: int, weight: torch.Tensor, bias: Optional
 
 
 def ssm_scan(xbc: torch.Tensor, proj: Optional[torch.Tensor], dt_off: int, dt_bias: Optional[torch.Tensor],
-             a_log: Optional[torch.Tensor], d_skip: Optional[torch.Tensor], state: torch.Tensor, y: torch.Tensor, heads: int,
+             a_log: Optional[torch.Tensor], d_skip: Optional[torch.Tensor], state: torch.Tensor, y: Optional[torch.Tensor], heads: int,
              vdim: int, n_state: int, groups: int, cu_seqlens: torch.Tensor, slots: torch.Tensor,
              fixed_decay: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence over every sequence's run of new tokens.  xbc float32 [T, heads*vdim + 2*groups*n_state]
     (x | B | C after convolution and silu); the raw step sizes are proj[:, dt_off:dt_off+heads];
-    state float32 [max_slots, heads, vdim, n_state] (a head's state column by column; rows may be strided); y float32 [T, heads*vdim].
+    state float32 [max_slots, heads, vdim, n_state] (a head's state column by column; rows may be strided); y float32 [T, heads*vdim],
+    or None: the states are walked on and no output is written.
     fixed_decay float32 [heads]: S <- fixed_decay[h] S + B x^T, y = S^T C instead (a constant decay per head, a step
     size of one, no skip term); proj and the per-head tensors are then not read and may be None."""
-    for t, what in ((xbc, "x, B and C"), (state, "the state"), (y, "the output")):
+    for t, what in ((xbc, "x, B and C"), (state, "the state")) + (((y, "the output"),) if y is not None else ()):
         want_f32(t, what)
     if fixed_decay is not None:
         want_f32(fixed_decay, "the decays")
@@ -72,6 +73,13 @@ def ssm_scan(xbc: torch.Tensor, proj: Optional[torch.Tensor], dt_off: int, dt_bi
 
 
 MAX_ROTATED_HEAD = 256      # csrc/ssm.cu RET_MAX_DIM
+SCAN_WARPS_PER_SM = 16      # warps of the recurrence kernel an SM holds: two blocks of eight (128 registers a thread)
+
+
+def scan_warps(n_seqs: int, heads: int, vdim: int) -> int:
+    """Warps that `ssm_scan` launches for this many sequences (a warp owns four columns of a head's state and walks
+    its sequence's run token by token)."""
+    return int(load_kernel(_LIB).tq_ssm_scan_warps(c_int(n_seqs), c_int(heads), c_int(vdim)))
 
 
 def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor,
@@ -109,3 +117,23 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: Op
                                         c_int(code(out.dtype)), c_int(T), c_int(inner), c_int(norm_groups), c_float(eps),
                                         c_int(1 if gate_after else 0), stream()))
     return out
+
+
+def retention_combine(state: torch.Tensor, slots: torch.Tensor, ends: torch.Tensor, starts: torch.Tensor,
+                      seq_chunks: torch.Tensor, cu_chunks: torch.Tensor, decay: torch.Tensor) -> None:
+    """Chunks of long runs that `ssm_scan(fixed_decay=)` walked side by side from zero states: from the states they
+    reached (ends [chunks, heads, vdim, n]) and the sequences' kept states (state [slots, heads, vdim, n], rows by
+    `slots`), the states each chunk should have started from (starts, like ends) and the sequences' new kept states.
+    Sequence s owns chunks seq_chunks[s]..seq_chunks[s+1]; chunk c the tokens cu_chunks[c]..cu_chunks[c+1]."""
+    for t, what in ((state, "the state"), (ends, "the chunks' states"), (starts, "the chunks' starts"), (decay, "the decays")):
+        want_f32(t, what)
+    for t, what in ((slots, "slots"), (seq_chunks, "the sequences' chunks"), (cu_chunks, "the chunks' tokens")):
+        want_int32(t, what)
+    heads = state.shape[1]
+    if ends.shape != starts.shape or ends.shape[1:] != state.shape[1:] or not (ends.is_contiguous() and starts.is_contiguous()) \
+            or not state[0].is_contiguous() or decay.numel() != heads or cu_chunks.numel() != ends.shape[0] + 1:
+        raise KernelError("retention_combine: the chunks' states must be dense and shaped like the kept state's rows")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_retention_combine(ctypes_ptr(state), c_longlong(state.stride(0)), ptr(slots), ptr(ends), ptr(starts),
+                                         ptr(seq_chunks), ptr(cu_chunks), ptr(decay), c_int(seq_chunks.shape[0] - 1),
+                                         c_int(heads), c_int(state[0, 0].numel()), stream()))

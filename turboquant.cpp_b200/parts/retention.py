@@ -42,6 +42,7 @@ class RetentionMixer(Mixer):
         self.k_scale = float(k_scale) if k_scale is not None else float(dim) ** -0.5
         self.qk, self.inner = self.heads * self.dim, self.heads * self.vdim
         self.w_in = self.w_o = self.decay = None
+        self._sm_count: Optional[int] = None
 
     # rows of the fused input projection: [q | k | v | g]
     @property
@@ -79,6 +80,42 @@ class RetentionMixer(Mixer):
         """The fused input projection's weight ([q | k | v | g] rows): see `forward(projected=...)`."""
         return self.w_in
 
+    MIN_CHUNK = 64           # the shortest chunk worth cutting a run into
+
+    def _chunks(self, ctx: StepContext):
+        """None, or how this step's runs are cut into chunks for the recurrence: (token offsets of the chunks
+        [chunks + 1], chunk numbers [chunks], each sequence's chunks [sequences + 1]) on the device.  The recurrence
+        kernel walks a run token by token with a warp per four columns of a head's state; where those warps fill
+        less than half of the GPU and a run is long, cutting the runs fills it, at the price of walking them once
+        more for the states alone (half the work of a walk with outputs).  The plan depends on the step's runs and
+        on heads and vdim only, and is kept for the step's other layers."""
+        lens = list(ctx.host_q_lens)
+        if not lens or len(lens) != ctx.n_seqs or max(lens) < 2 * self.MIN_CHUNK:
+            return None
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(ctx.device).multi_processor_count
+        cuts = self._sm_count * KS.SCAN_WARPS_PER_SM // KS.scan_warps(len(lens), self.heads, self.vdim)
+        if cuts < 2:
+            return None
+        size = max(self.MIN_CHUNK, -(-max(lens) // cuts))
+        size = -(-size // 16) * 16
+        if max(lens) < 2 * size:
+            return None
+        key = f"retention_chunks_{size}"
+        plan = ctx.carry.get(key) if ctx.carry is not None else None
+        if plan is None:
+            cu, seq_chunks, at = [0], [0], 0
+            for n in lens:
+                for c0 in range(0, n, size):
+                    cu.append(at + min(n, c0 + size))
+                at += n
+                seq_chunks.append(len(cu) - 1)
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32).to(ctx.device, non_blocking=True)
+            plan = (i32(cu), torch.arange(len(cu) - 1, dtype=torch.int32, device=ctx.device), i32(seq_chunks))
+            if ctx.carry is not None:
+                ctx.carry[key] = plan
+        return plan
+
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache, projected: Optional[torch.Tensor] = None,
                 offset: int = 0) -> torch.Tensor:
         """projected: float32 rows of a wider product that hold this mixer's [q | k | v | g] from column `offset`."""
@@ -91,8 +128,22 @@ class RetentionMixer(Mixer):
                              pe.freq if pe is not None and pe.dims else None, pe.dims if pe is not None else 0,
                              pe is not None and pe.halves, self.k_scale, ctx.positions, self.heads, self.dim, self.vdim)
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
-        KS.ssm_scan(xbc, None, 0, None, None, None, S, y, self.heads, self.vdim, self.dim, self.heads, ctx.cu_seqlens,
-                    ctx.slots, fixed_decay=self.decay)
+        plan = self._chunks(ctx)
+        if plan is None:
+            KS.ssm_scan(xbc, None, 0, None, None, None, S, y, self.heads, self.vdim, self.dim, self.heads, ctx.cu_seqlens,
+                        ctx.slots, fixed_decay=self.decay)
+        else:
+            # long runs on few blocks: the chunks of a run side by side from zero states, the states they should have
+            # started from out of the states they reached, and the chunks once more from those for the outputs
+            cu_chunks, chunk_ids, seq_chunks = plan
+            n_chunks = chunk_ids.shape[0]
+            ends = torch.zeros((n_chunks,) + tuple(S.shape[1:]), dtype=torch.float32, device=dev)
+            starts = torch.empty_like(ends)
+            scan = lambda st, out: KS.ssm_scan(xbc, None, 0, None, None, None, st, out, self.heads, self.vdim, self.dim, self.heads,
+                                               cu_chunks, chunk_ids, fixed_decay=self.decay)
+            scan(ends, None)                     # the states alone: half the work of a walk with outputs
+            KS.retention_combine(S, ctx.slots, ends, starts, seq_chunks, cu_chunks, self.decay)
+            scan(starts, y)
         g = torch.empty((T, self.inner), dtype=ctx.act_dtype, device=dev)
         KS.gated_group_norm(y, proj, offset + 2 * self.qk + self.inner, None, self.heads, self.eps, g, gate_after=True)
         return linear(g, self.w_o, out_dtype=torch.float32)
