@@ -275,6 +275,53 @@ def test_retention_in_chunks_side_by_side(case):
     assert float(state[1].min()) == 7.0 and float(state[3].max()) == 7.0
 
 
+@pytest.mark.parametrize("case", RET_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_token_of_every_sequence_in_one_launch(case, dtype):
+    """Decode steps through the one-launch form: three sequences at different positions, in slots that held other
+    values, after a prompt through the kernels for runs; rotation, recurrence, unit norm and gate against the plain
+    steps, and slots of other sequences left alone."""
+    from turboquant_cpp_b200.kernels import ssm as KS
+    heads, dk, dv, decay, rot = case
+    rng = np.random.default_rng(heads + dk + dv)
+    m = {"decay": list(decay), "rot": rot, "heads": heads, "dim": dk, "vdim": dv}
+    qk, inner = heads * dk, heads * dv
+    lead = 5
+    lens, prompt = {0: 40, 1: 23, 2: 31}, {0: 17, 1: 0, 2: 30}
+    proj = {s: host(dev(rng.standard_normal((n, lead + 2 * qk + 2 * inner)))) for s, n in lens.items()}
+    want = {}
+    for s, n in lens.items():
+        pr = proj[s][:, lead:]
+        o, _ = P.retention_core(pr[:, :qk].reshape(n, heads, dk), pr[:, qk:2 * qk].reshape(n, heads, dk),
+                                pr[:, 2 * qk:2 * qk + inner].reshape(n, heads, dv), m)
+        want[s] = (P.unit(o, 2e-4).reshape(n, inner) * P.silu(pr[:, 2 * qk + inner:]))
+    state = torch.full((6, heads, dv, dk), 7.0, dtype=torch.float32, device=DEV)
+    slots = {0: 4, 1: 0, 2: 2}
+    decay_dev = dev(np.array(decay))
+    f, rd = frequencies(rot), rot["dims"] if rot else 0
+    for s, n in prompt.items():                               # prompts through the kernels for runs
+        state[slots[s]].zero_()
+        if n == 0:
+            continue
+        xbc = torch.empty((n, inner + 2 * qk), dtype=torch.float32, device=DEV)
+        KS.retention_prepare(dev(proj[s][:n]), lead, lead + qk, lead + 2 * qk, xbc, f, rd, True, dk ** -0.5, i32(list(range(n))), heads, dk, dv)
+        KS.ssm_scan(xbc, None, 0, None, None, None, state, torch.empty((n, inner), dtype=torch.float32, device=DEV), heads, dv, dk,
+                    heads, i32([0, n]), i32([slots[s]]), fixed_decay=decay_dev)
+    at = dict(prompt)
+    tol = 3e-5 if dtype == torch.float32 else 1e-2
+    while any(at[s] < lens[s] for s in lens):
+        live = [s for s in lens if at[s] < lens[s]]
+        pr = dev(np.stack([proj[s][at[s]] for s in live]))
+        out = torch.empty((len(live), inner), dtype=dtype, device=DEV)
+        KS.retention_step(pr, lead, lead + qk, lead + 2 * qk, lead + 2 * qk + inner, f, rd, True, dk ** -0.5,
+                          i32([at[s] for s in live]), state, i32([slots[s] for s in live]), decay_dev, out, heads, dk, dv, 2e-4)
+        for i, s in enumerate(live):
+            ref = want[s][at[s]]
+            assert np.abs(host(out[i]) - ref).max() < tol * max(1.0, np.abs(ref).max()), (s, at[s])
+            at[s] += 1
+    assert float(state[1].min()) == 7.0 and float(state[3].max()) == 7.0 and float(state[5].min()) == 7.0
+
+
 def test_a_far_token_speaks_through_a_head_that_forgets_nothing():
     """A key along one direction at position 3, a query along it 900 tokens later, a decay of one: the output holds that
     token's value at full weight; the head beside it, with a decay of 0.9, has lost it."""

@@ -526,3 +526,111 @@ TQ_EXPORT int tq_retention_combine(float* state, long long slot_stride, const in
     TQ_CHECK_LAUNCH("retention_combine");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// retention_step: a decode step of retention in one launch, for steps in which every sequence brings one token
+// (token t is sequence t).  Grid (token, head), up to sixteen warps.  From the token's row of the fused projection
+// [.. q .. k .. v .. g ..]: q' = rotate(q), k' = rotate(k) * k_scale (as retention_prepare), then over the head's
+// state, kept column by column [dv][dk]:  S[c] <- decay_h S[c] + k' v_c,  o_c = S[c] . q'  (a warp per group of columns, lanes
+// over the rows), then out = o / sqrt(mean(o^2) + eps) * silu(g) (the unit norm over the head, then the gate).
+// All float32; out in the activation dtype.  The state is read and written once.
+// ---------------------------------------------------------------------------------------
+#define RET_STEP_COLS 4
+template <typename TO>
+__global__ void __launch_bounds__(512)
+retention_step_kernel(const float* __restrict__ proj, int P, int q_off, int k_off, int v_off, int g_off,
+                      const float* __restrict__ freq, int rot_dims, int halves, float k_scale,
+                      const int* __restrict__ positions, float* __restrict__ state, long long slot_stride,
+                      const int* __restrict__ slots, const float* __restrict__ decay, TO* __restrict__ out, int heads,
+                      int dk, int dv, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float s_raw[2][RET_MAX_DIM], s_q[RET_MAX_DIM], s_k[RET_MAX_DIM], scratch[33];
+    extern __shared__ float s_o[];     // [dv]
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* row = proj + (size_t)t * P;
+    for (int e = tid; e < dk; e += blockDim.x) {
+        s_raw[0][e] = row[q_off + (size_t)h * dk + e];
+        s_raw[1][e] = row[k_off + (size_t)h * dk + e];
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    for (int e = tid; e < dk; e += blockDim.x) {
+        s_q[e] = tq_rotated(s_raw[0], e, rot_dims, halves, freq, pos);
+        s_k[e] = tq_rotated(s_raw[1], e, rot_dims, halves, freq, pos) * k_scale;
+    }
+    __syncthreads();
+    const float d = decay[h];
+    float* S = state + (size_t)slots[t] * slot_stride + (size_t)h * dv * dk;
+    const float* vr = row + v_off + (size_t)h * dv;
+    // a warp takes RET_STEP_COLS columns at a time, their loads in flight together (a step is one pass over a state
+    // that nothing else reads: what it costs is the latency of that pass, not its bytes)
+    const int n_warps = blockDim.x >> 5;
+    for (int c0 = warp * RET_STEP_COLS; c0 < dv; c0 += n_warps * RET_STEP_COLS) {
+        float vc[RET_STEP_COLS], acc[RET_STEP_COLS];
+#pragma unroll
+        for (int j = 0; j < RET_STEP_COLS; ++j) {
+            vc[j] = c0 + j < dv ? vr[c0 + j] : 0.f;
+            acc[j] = 0.f;
+        }
+        // all of the group's state in registers first (up to RET_MAX_DIM / 32 rows a lane and column), then the updates
+        float sv[RET_MAX_DIM / 32][RET_STEP_COLS];
+#pragma unroll
+        for (int i = 0; i < RET_MAX_DIM / 32; ++i) {
+            const int r = lane + 32 * i;
+#pragma unroll
+            for (int j = 0; j < RET_STEP_COLS; ++j) sv[i][j] = (r < dk && c0 + j < dv) ? S[(size_t)(c0 + j) * dk + r] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < RET_MAX_DIM / 32; ++i) {
+            const int r = lane + 32 * i;
+            if (r < dk) {
+                const float kr = s_k[r], qr = s_q[r];
+#pragma unroll
+                for (int j = 0; j < RET_STEP_COLS; ++j) {
+                    const float v = d * sv[i][j] + kr * vc[j];
+                    if (c0 + j < dv) S[(size_t)(c0 + j) * dk + r] = v;
+                    acc[j] += v * qr;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < RET_STEP_COLS; ++j) acc[j] = tq_warp_sum(acc[j]);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < RET_STEP_COLS; ++j)
+                if (c0 + j < dv) s_o[c0 + j] = acc[j];
+        }
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int c = tid; c < dv; c += blockDim.x) ss += s_o[c] * s_o[c];
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)dv + eps);
+    const float* gr = row + g_off + (size_t)h * dv;
+    for (int c = tid; c < dv; c += blockDim.x) {
+        const float z = gr[c];
+        out[((size_t)t * heads + h) * dv + c] = tq_from_float<TO>(s_o[c] * rs * (z / (1.0f + expf(-z))));
+    }
+}
+
+TQ_EXPORT int tq_retention_step(const float* proj, int P, int q_off, int k_off, int v_off, int g_off, const float* freq,
+                                int rot_dims, int halves, float k_scale, const int* positions, float* state,
+                                long long slot_stride, const int* slots, const float* decay, void* out, int out_dtype, int T_,
+                                int heads, int dk, int dv, float eps, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && heads <= 65535 && dk >= 1 && dk <= RET_MAX_DIM && dv >= 1 && dv <= 8192,
+               "retention_step: bad sizes %d %d %d", heads, dk, dv);
+    TQ_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && g_off >= 0 && q_off + heads * dk <= P && k_off + heads * dk <= P &&
+               v_off + heads * dv <= P && g_off + heads * dv <= P, "retention_step: the heads lie outside the projection's rows of %d", P);
+    TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
+               "retention_step: %d rotated elements of a head of %d", rot_dims, dk);
+    const int groups = (dv + RET_STEP_COLS - 1) / RET_STEP_COLS;                  // a warp a group, up to sixteen
+    const int threads = 32 * (groups >= 16 ? 16 : (groups >= 8 ? 8 : (groups >= 4 ? 4 : (groups >= 2 ? 2 : 1))));
+    TQ_DISPATCH(out_dtype, TO,
+        (tq_launch(dim3(T_, heads), threads, (size_t)dv * sizeof(float), stream)(retention_step_kernel<TO>, proj, P, q_off, k_off, v_off,
+            g_off, freq, rot_dims, halves, k_scale, positions, state, slot_stride, slots, decay, (TO*)out, heads, dk, dv, eps)));
+    TQ_CHECK_LAUNCH("retention_step");
+    return 0;
+}

@@ -137,3 +137,31 @@ def retention_combine(state: torch.Tensor, slots: torch.Tensor, ends: torch.Tens
     check(_LIB, lib.tq_retention_combine(ctypes_ptr(state), c_longlong(state.stride(0)), ptr(slots), ptr(ends), ptr(starts),
                                          ptr(seq_chunks), ptr(cu_chunks), ptr(decay), c_int(seq_chunks.shape[0] - 1),
                                          c_int(heads), c_int(state[0, 0].numel()), stream()))
+
+
+def retention_step(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: int, freq: Optional[torch.Tensor],
+                   rot_dims: int, halves: bool, k_scale: float, positions: torch.Tensor, state: torch.Tensor,
+                   slots: torch.Tensor, decay: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int, eps: float) -> torch.Tensor:
+    """One token of every sequence through retention in one launch (token t is sequence t, its state the row
+    slots[t]): `retention_prepare`, `ssm_scan(fixed_decay=)` and `gated_group_norm(gate_after=True)` without a weight,
+    for rows of the fused projection proj float32 [T, P] that hold q, k (heads x dk) and v, g (heads x dv) from the
+    given columns.  state float32 [slots, heads, dv, dk]; out [T, heads*dv]."""
+    want_f32(proj, "the projection")
+    want_f32(state, "the state")
+    want_f32(decay, "the decays")
+    want_int32(positions, "positions")
+    want_int32(slots, "slots")
+    T = proj.shape[0]
+    if tuple(state.shape[1:]) != (heads, dv, dk) or not state[0].is_contiguous() or out.shape != (T, heads * dv) \
+            or slots.numel() != T or positions.numel() != T or decay.numel() != heads:
+        raise KernelError("retention_step: the state must be [slots, heads, vdim, dim] with dense rows, one slot and position a token")
+    if freq is not None:
+        want_f32(freq, "frequencies")
+        if 2 * freq.numel() != rot_dims:
+            raise KernelError("retention_step: one frequency per rotated pair")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_retention_step(ptr(proj), c_int(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), c_int(g_off),
+                                      ptr(freq), c_int(rot_dims), c_int(1 if halves else 0), c_float(k_scale), ptr(positions),
+                                      ctypes_ptr(state), c_longlong(state.stride(0)), ptr(slots), ptr(decay), ptr(out),
+                                      c_int(code(out.dtype)), c_int(T), c_int(heads), c_int(dk), c_int(dv), c_float(eps), stream()))
+    return out

@@ -14,6 +14,7 @@ constant decay, a step size of one and one group per head (B = k, C = q, x = v).
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -81,6 +82,8 @@ class RetentionMixer(Mixer):
         return self.w_in
 
     MIN_CHUNK = 64           # the shortest chunk worth cutting a run into
+    # decode steps with at least this many (sequence, head) pairs take the one-launch form (TQ_RETENTION_STEP_MIN_BLOCKS)
+    STEP_MIN_BLOCKS = int(os.environ.get("TQ_RETENTION_STEP_MIN_BLOCKS", "0"))
 
     def _chunks(self, ctx: StepContext):
         """None, or how this step's runs are cut into chunks for the recurrence: (token offsets of the chunks
@@ -123,6 +126,14 @@ class RetentionMixer(Mixer):
         proj = projected if projected is not None else linear(xn, self.w_in, out_dtype=torch.float32)
         S = cache.state.unflatten(1, (self.heads, self.vdim, self.dim))          # column by column
         pe = self.position
+        if ctx.max_q_len == 1 and ctx.n_seqs == T and T * self.heads >= self.STEP_MIN_BLOCKS:
+            # every sequence brings one token: rotation, the state's update and read-out, unit norm and gate in one launch
+            g = torch.empty((T, self.inner), dtype=ctx.act_dtype, device=dev)
+            KS.retention_step(proj, offset, offset + self.qk, offset + 2 * self.qk, offset + 2 * self.qk + self.inner,
+                              pe.freq if pe is not None and pe.dims else None, pe.dims if pe is not None else 0,
+                              pe is not None and pe.halves, self.k_scale, ctx.positions, S, ctx.slots, self.decay, g,
+                              self.heads, self.dim, self.vdim, self.eps)
+            return linear(g, self.w_o, out_dtype=torch.float32)
         xbc = torch.empty((T, self.inner + 2 * self.qk), dtype=torch.float32, device=dev)
         KS.retention_prepare(proj, offset, offset + self.qk, offset + 2 * self.qk, xbc,
                              pe.freq if pe is not None and pe.dims else None, pe.dims if pe is not None else 0,
