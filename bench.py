@@ -377,14 +377,14 @@ LUMEVIK_SIZES = {
 def sisepel_config(width, layers, heads, kv_heads, dim, window, r_heads, r_dim, r_vdim, ff, experts, top, e_ff, s_ff, side, vocab):
     """Layers in pairs: a dense feed-forward, then routed experts; every layer has windowed attention and retention
     side by side and a token input of its own."""
-    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
                       "mask": {"size": window},
                       "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
              "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"base": 10000.0, "dims": r_dim},
-                       "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * i / max(1, r_heads - 1)) for i in range(r_heads)]}}
+                       "decay": [1.0 - 2.0 ** (-4.0 - 5.0 * i / max(1, r_heads - 1)) for i in range(r_heads)]}}
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": s_ff}, "router": {"experts": experts, "top": top}}
-    return {"architecture": "Sisepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+    return {"architecture": "Sisepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
             "token_side": {"dim": side},
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(layers)]}
 

@@ -171,7 +171,7 @@ RET_CASES = [
     (2, 64, 64, (0.5, 0.9990234375), {"dims": 32, "base": 1e4}),
     (1, 200, 3, (0.99,), None),
     (5, 5, 33, (0.1, 0.3, 0.5, 0.7, 0.9), {"dims": 4, "base": 9.0}),
-    (4, 32, 128, (0.96875, 0.99, 0.999, 0.9999), {"dims": 32, "base": 1e6}),
+    (4, 96, 128, (0.9375, 0.99, 0.999, 0.9999), {"dims": 64, "base": 2e5}),
 ]
 
 
