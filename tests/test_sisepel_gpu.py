@@ -335,6 +335,32 @@ def test_greedy_generation_through_the_entry_point(folders, dtype):
             toks.append(t)
 
 
+def test_command_line_on_a_folder_and_on_random_weights(folders, tmp_path):
+    """bin/quant on a folder of the design gives the entry point's greedy tokens; --info names the design; --random
+    CONFIG --seed-weights N builds and runs a model of the configuration, another seed another model; --profile
+    prints its buckets."""
+    import turboquant_cpp_b200 as tq
+    cfg, folder = CONFIGS["a"], folders["a"]
+    prompts = [tokens_for(cfg, n, 60 + n) for n in (3, 21)]
+    quant = [sys.executable, os.path.join(ROOT, "bin", "quant")]
+    common = ["-n", "7", "-T", "0", "--dtype", "float32"]
+    tok_file, cfg_file = str(tmp_path / "prompts.txt"), str(tmp_path / "cfg.json")
+    open(tok_file, "w").write("\n".join(" ".join(map(str, q)) for q in prompts) + "\n")
+    json.dump(cfg, open(cfg_file, "w"))
+    r = subprocess.run(quant + [folder] + common + ["--tokens-file", tok_file], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    with tq.Model(folder, temperature=0.0, max_tokens=7, dtype="float32") as m:
+        want = m.generate_batch(prompts)
+    assert [[int(t) for t in l.split()] for l in r.stdout.strip().splitlines()] == want
+    info = subprocess.run(quant + [folder, "--info"], capture_output=True, text=True, timeout=600)
+    assert info.returncode == 0 and "Sisepel" in info.stdout
+    runs = [subprocess.run(quant + ["--random", cfg_file, "--seed-weights", str(seed)] + common + ["--tokens-file", tok_file, "--profile"],
+                           capture_output=True, text=True, timeout=600) for seed in (3, 4)]
+    assert all(x.returncode == 0 for x in runs), runs[0].stderr + runs[1].stderr
+    assert len(runs[0].stdout.strip().splitlines()) == 2 and runs[0].stdout != runs[1].stdout
+    assert any(l.startswith("[Profile ") and "matmul=" in l for l in runs[0].stderr.splitlines())
+
+
 def test_trace_replay_as_a_user_runs_it(folders, tmp_path):
     cfg, folder = CONFIGS["c"], folders["c"]
     reqs = {"a": tokens_for(cfg, 45, 50), "b": tokens_for(cfg, 140, 51), "c": tokens_for(cfg, 1, 52)}
