@@ -543,7 +543,7 @@ def lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, wa
                                                          "window": window, "dense_ff": ff, "experts": E, "top": top,
                                                          "expert_ff": e_ff, "shared_ff": s_ff})
             if args.kernel_table:
-                kernel_table(tq, model, rng, V, 8, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
+                kernel_table(tq, model, rng, V, args.batch, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
             del model
             gc.collect()
             torch.cuda.empty_cache()
@@ -579,7 +579,7 @@ def sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, wa
                 conf.update(retention={"heads": rh, "dim": rd, "vdim": rv}, token_input=side)
             entry[who] = dict(measure(model, V), config=conf)
             if args.kernel_table:
-                kernel_table(tq, model, rng, V, 8, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
+                kernel_table(tq, model, rng, V, args.batch, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
             del model
             gc.collect()
             torch.cuda.empty_cache()
