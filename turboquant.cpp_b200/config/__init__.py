@@ -5,7 +5,8 @@ from .registry import (Architecture, register_architecture, unregister_architect
                        parse_config, load_config)
 from .qwen2_moe import Qwen2MoeConfig
 from .nuforax import NuforaxConfig
+from .tasadra import TasadraConfig
 
 __all__ = ["ConfigError", "KeyReader", "read_config_json", "Architecture", "register_architecture",
            "unregister_architecture", "registered_architectures", "lookup_architecture",
-           "architecture_name", "parse_config", "load_config", "Qwen2MoeConfig", "NuforaxConfig"]
+           "architecture_name", "parse_config", "load_config", "Qwen2MoeConfig", "NuforaxConfig", "TasadraConfig"]

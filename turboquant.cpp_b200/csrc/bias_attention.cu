@@ -3,7 +3,8 @@
 //
 //   score(i, j) = cap(q_i . k_j * scale) + bias[min(i - j, far)][head]   (bias: a table per distance, or none;
 //                                                                          cap(s) = softcap * tanh(s / softcap), or s if softcap is 0)
-//   i sees j    iff j <= i and (window == 0 or i - j < window or j < keep_first)
+//   i sees j    iff j <= i and (window == 0 or i - j < window or j < keep_first);
+//               with cells (cell > 0) instead iff j <= i and floor(i / cell) = floor(j / cell)
 //   p_j         = exp(score_j) / (exp(sink[head]) + sum over the visible j of exp(score_j))   (sink: per head, or none)
 //   out_i       = sum_j p_j v_j
 //
@@ -77,15 +78,21 @@ TQ_EXPORT int tq_bias_kv_write(const float* qkv, void* q_out, void* cache, int a
 }
 
 // ---------------------------------------------------------------------------------------
-// The same split with a rotation and a unit norm on the way: queries and keys are rotated by their token's position
-// (the first rot_dims elements of each head, pairs of neighbours or of halves, angle = position * freq[i] in fp32), then
-// each head is divided by its root mean square (unit_eps > 0: x / sqrt(mean(x^2) + unit_eps); 0: left as it is).
+// The same split with norms and rotations on the way.  Per query and key head, in this order: an RMS norm with a weight
+// shared by the heads (q_norm_w / k_norm_w fp32 [dk], x / sqrt(mean(x^2) + norm_eps) * w; null: none), the rotation
+// by the token's position (the first rot_dims elements of each head, pairs of neighbours or of halves, angle =
+// position * freq[i] in fp32, cos and sin multiplied by `mag`), then a unit norm (unit_eps > 0:
+// x / sqrt(mean(x^2) + unit_eps); 0: left as it is).  Values: kv head g caches value head g / v_share of the row
+// (v_share > 1: neighbouring key heads keep the same values), turned by position * v_freq[m] over all dv elements
+// in the same pairing (v_freq fp32 [dv / 2]; null: as they are).
 // Grid (token, groups of four query and key heads): a warp per head; the blocks of a token share out the copy of the values.
 // ---------------------------------------------------------------------------------------
 template <typename TA>
 __global__ void __launch_bounds__(128)
 bias_kv_write_rot_kernel(const float* __restrict__ qkv, int row_stride, TA* __restrict__ q_out, TA* __restrict__ cache,
-                         const float* __restrict__ freq, int rot_dims, int halves, float unit_eps,
+                         const float* __restrict__ freq, int rot_dims, int halves, float mag, float unit_eps,
+                         const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float norm_eps,
+                         const float* __restrict__ v_freq, int v_share,
                          const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                          const int* __restrict__ page_table, int table_stride, int page_size,
                          int nh, int nkv, int dk, int dv, int n_seqs, int n_pages) {
@@ -105,20 +112,30 @@ bias_kv_write_rot_kernel(const float* __restrict__ qkv, int row_stride, TA* __re
     if (cache != nullptr)
         for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
             const int g = i / dv, e = i % dv;
-            cache[(((size_t)page * nkv + g) * page_size + slot) * dr + dk + e] = tq_from_float<TA>(row[nq + nk + i]);
+            const float* vh = row + nq + nk + (size_t)(g / v_share) * dv;
+            const float v = v_freq ? tq_rotated(vh, e, dv & ~1, halves, v_freq, pos) : vh[e];
+            cache[(((size_t)page * nkv + g) * page_size + slot) * dr + dk + e] = tq_from_float<TA>(v);
         }
     const int head = blockIdx.y * 4 + warp;
-    if (head >= nh + nkv) return;
+    if (head >= nh + nkv || (head >= nh && cache == nullptr)) return;      // without a cache the rows may hold queries only
     const float* src = row + (size_t)head * dk;                // keys follow the queries in the row
     float* sh = s_head[warp];
-    for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+    const float* nw = head < nh ? q_norm_w : k_norm_w;
+    if (nw != nullptr) {
+        float ss = 0.f;
+        for (int e = lane; e < dk; e += 32) { const float x = src[e]; ss += x * x; }
+        const float rs = 1.0f / sqrtf(tq_warp_sum(ss) / (float)dk + norm_eps);
+        for (int e = lane; e < dk; e += 32) sh[e] = src[e] * rs * nw[e];
+    } else {
+        for (int e = lane; e < dk; e += 32) sh[e] = src[e];
+    }
     __syncwarp();
     float v[BA_EPL];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < BA_EPL; ++j) {
         const int e = lane + 32 * j;
-        v[j] = e < dk ? tq_rotated(sh, e, rot_dims, halves, freq, pos) : 0.f;
+        v[j] = e < dk ? tq_rotated(sh, e, rot_dims, halves, freq, pos) * (e < rot_dims ? mag : 1.0f) : 0.f;
         ss += v[j] * v[j];
     }
     float rs = 1.f;
@@ -133,20 +150,120 @@ bias_kv_write_rot_kernel(const float* __restrict__ qkv, int row_stride, TA* __re
     }
 }
 
-// qkv: fp32 rows of row_stride floats that begin with [q | k | v]; freq: fp32 [rot_dims / 2] (null with rot_dims 0).
+// qkv: fp32 rows of row_stride floats that begin with [q | k | v] (v: nkv / v_share heads); freq: fp32 [rot_dims / 2]
+// (null with rot_dims 0).
 TQ_EXPORT int tq_bias_kv_write_rot(const float* qkv, int row_stride, void* q_out, void* cache, int act_dtype,
-                                   const float* freq, int rot_dims, int halves, float unit_eps, const int* positions,
+                                   const float* freq, int rot_dims, int halves, float mag, float unit_eps,
+                                   const float* q_norm_w, const float* k_norm_w, float norm_eps, const float* v_freq,
+                                   int v_share, const int* positions,
                                    const int* seq_of_token, const int* page_table, int table_stride, int page_size,
                                    int T_, int nh, int nkv, int dk, int dv, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(nh >= 1 && nkv >= 1 && dk >= 1 && dv >= 1 && dk <= BA_MAX_DIM, "bias_kv_write_rot: bad sizes %d %d %d %d", nh, nkv, dk, dv);
-    TQ_REQUIRE(row_stride >= nh * dk + nkv * (dk + dv), "bias_kv_write_rot: rows of %d floats do not hold the heads", row_stride);
+    TQ_REQUIRE(v_share >= 1 && nkv % v_share == 0, "bias_kv_write_rot: %d key heads cannot share values in groups of %d", nkv, v_share);
+    TQ_REQUIRE(row_stride >= nh * dk + (cache ? nkv * dk + nkv / v_share * dv : 0), "bias_kv_write_rot: rows of %d floats do not hold the heads", row_stride);
     TQ_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
                "bias_kv_write_rot: %d rotated elements of a head of %d", rot_dims, dk);
+    TQ_REQUIRE(v_freq == nullptr || dv % 2 == 0, "bias_kv_write_rot: values of %d elements cannot be rotated in pairs", dv);
     TQ_DISPATCH(act_dtype, TA,
         (tq_launch(dim3(T_, (nh + nkv + 3) / 4), 128, 0, stream)(bias_kv_write_rot_kernel<TA>, qkv, row_stride, (TA*)q_out, (TA*)cache, freq, rot_dims,
-            halves, unit_eps, positions, seq_of_token, page_table, table_stride, page_size, nh, nkv, dk, dv, n_seqs, n_pages)));
+            halves, mag, unit_eps, q_norm_w, k_norm_w, norm_eps, v_freq, v_share, positions, seq_of_token, page_table, table_stride, page_size,
+            nh, nkv, dk, dv, n_seqs, n_pages)));
     TQ_CHECK_LAUNCH("bias_kv_write_rot");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// What follows the weighted sums of two designs' attention, per (token, head), in fp32:
+//   tq_heads_unrotate_gate   a head's output turned back by its own position (pair m by -position * v_freq[m] over all
+//                            dv elements; null: not turned), times sigmoid of the head's gate logit (one per head, from
+//                            a projection's fp32 rows)
+//   tq_diff_combine          two maps' outputs a1, a2 of a head over the same values: o = a1 - lambda * a2,
+//                            o / sqrt(mean(o^2) + eps) * out_scale, times sigmoid of the element's gate logit.  The
+//                            maps lie as the attention kernels leave them with the maps of a key/value head's queries
+//                            side by side: head (g, map, j) at g * 2 * per + map * per + j, per = heads / kv heads.
+// A warp per (token, head), four a block.
+// ---------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128)
+heads_unrotate_gate_kernel(const TA* __restrict__ o, const float* __restrict__ gates, int gate_stride, int gate_off,
+                           const float* __restrict__ v_freq, int halves, const int* __restrict__ positions,
+                           TA* __restrict__ out, int T_, int nh, int dv) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float s_head[4][BA_MAX_DIM];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t item = (size_t)blockIdx.x * 4 + warp;
+    if (item >= (size_t)T_ * nh) return;
+    const int t = (int)(item / nh), h = (int)(item % nh);
+    float* sh = s_head[warp];
+    const TA* src = o + item * dv;
+    for (int e = lane; e < dv; e += 32) sh[e] = tq_to_float(src[e]);
+    __syncwarp();
+    const float z = gates[(size_t)t * gate_stride + gate_off + h];
+    const float gate = 1.0f / (1.0f + expf(-z));
+    const int pos = positions[t];
+    for (int e = lane; e < dv; e += 32) {
+        const float v = v_freq ? tq_rotated(sh, e, dv & ~1, halves, v_freq, -pos) : sh[e];
+        out[item * dv + e] = tq_from_float<TA>(v * gate);
+    }
+}
+
+TQ_EXPORT int tq_heads_unrotate_gate(const void* o, int act_dtype, const float* gates, int gate_stride, int gate_off,
+                                     const float* v_freq, int halves, const int* positions, void* out, int T_, int nh, int dv,
+                                     cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(nh >= 1 && dv >= 1 && dv <= BA_MAX_DIM, "heads_unrotate_gate: %d heads of %d values", nh, dv);
+    TQ_REQUIRE(gate_off >= 0 && gate_off + nh <= gate_stride, "heads_unrotate_gate: the gates lie outside their rows");
+    TQ_REQUIRE(v_freq == nullptr || dv % 2 == 0, "heads_unrotate_gate: values of %d elements cannot be rotated in pairs", dv);
+    const long long items = (long long)T_ * nh;
+    TQ_DISPATCH(act_dtype, TA,
+        (tq_launch((unsigned)((items + 3) / 4), 128, 0, stream)(heads_unrotate_gate_kernel<TA>, (const TA*)o, gates, gate_stride, gate_off,
+            v_freq, halves, positions, (TA*)out, T_, nh, dv)));
+    TQ_CHECK_LAUNCH("heads_unrotate_gate");
+    return 0;
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const TA* __restrict__ o, const float* __restrict__ gates, int gate_stride, int gate_off, float lambda,
+                    float eps, float out_scale, TA* __restrict__ out, int T_, int nh, int nkv, int dv) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t item = (size_t)blockIdx.x * 4 + warp;
+    if (item >= (size_t)T_ * nh) return;
+    const int t = (int)(item / nh), h = (int)(item % nh);
+    const int per = nh / nkv, g = h / per, j = h % per;
+    const TA* a1 = o + ((size_t)t * 2 * nh + (size_t)g * 2 * per + j) * dv;
+    const TA* a2 = a1 + (size_t)per * dv;
+    float v[BA_EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < BA_EPL; ++k) {
+        const int e = lane + 32 * k;
+        v[k] = e < dv ? tq_to_float(a1[e]) - lambda * tq_to_float(a2[e]) : 0.f;
+        ss += v[k] * v[k];
+    }
+    const float rs = out_scale / sqrtf(tq_warp_sum(ss) / (float)dv + eps);
+    const float* gr = gates + (size_t)t * gate_stride + gate_off + (size_t)h * dv;
+#pragma unroll
+    for (int k = 0; k < BA_EPL; ++k) {
+        const int e = lane + 32 * k;
+        if (e < dv) out[item * dv + e] = tq_from_float<TA>(v[k] * rs / (1.0f + expf(-gr[e])));
+    }
+}
+
+TQ_EXPORT int tq_diff_combine(const void* o, int act_dtype, const float* gates, int gate_stride, int gate_off, float lambda,
+                              float eps, float out_scale, void* out, int T_, int nh, int nkv, int dv, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(nh >= 1 && nkv >= 1 && nh % nkv == 0 && dv >= 1 && dv <= BA_MAX_DIM, "diff_combine: %d heads on %d of %d values", nh, nkv, dv);
+    TQ_REQUIRE(gate_off >= 0 && gate_off + nh * dv <= gate_stride, "diff_combine: the gates lie outside their rows");
+    const long long items = (long long)T_ * nh;
+    TQ_DISPATCH(act_dtype, TA,
+        (tq_launch((unsigned)((items + 3) / 4), 128, 0, stream)(diff_combine_kernel<TA>, (const TA*)o, gates, gate_stride, gate_off, lambda,
+            eps, out_scale, (TA*)out, T_, nh, nkv, dv)));
+    TQ_CHECK_LAUNCH("diff_combine");
     return 0;
 }
 
@@ -155,6 +272,9 @@ struct BaSpan {
     int n_first, start, count;
     __device__ __forceinline__ int at(int n) const { return n < n_first ? n : start + (n - n_first); }
 };
+// With cells (cell > 0) a query sees the positions of its own cell only: those from pos - pos % cell on, which is a
+// window of pos % cell + 1 positions.
+__device__ __forceinline__ int ba_window_at(int pos, int window, int cell) { return cell > 0 ? pos % cell + 1 : window; }
 __device__ __forceinline__ BaSpan ba_span(int pos, int window, int keep_first) {
     BaSpan s;
     s.start = window > 0 ? max(0, pos + 1 - window) : 0;
@@ -174,7 +294,7 @@ __global__ void __launch_bounds__(BA_WARPS * 32)
 bias_attention_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const float* __restrict__ bias, int far,
                       const float* __restrict__ sink, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
-                      int page_size, int window, int keep_first, float scale, float softcap, TA* __restrict__ out,
+                      int page_size, int window, int keep_first, int cell, float scale, float softcap, TA* __restrict__ out,
                       float* __restrict__ partial, int n_splits, int nh, int nkv, int dk, int dv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -184,7 +304,7 @@ bias_attention_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, co
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = h / (nh / nkv), dr = dk + dv;
     const int pos = positions[t];
-    const BaSpan span = ba_span(pos, window, keep_first);
+    const BaSpan span = ba_span(pos, ba_window_at(pos, window, cell), cell > 0 ? 0 : keep_first);
     const int per = (span.count + n_splits - 1) / n_splits;
     const int n0 = split * per, n1 = min(span.count, n0 + per);
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
@@ -285,7 +405,7 @@ __global__ void bias_attention_merge_kernel(const float* __restrict__ partial, i
 
 TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype, const float* bias, int far,
                                 const float* sink, const int* positions, const int* seq_of_token,
-                                const int* page_table, int table_stride, int page_size, int window, int keep_first,
+                                const int* page_table, int table_stride, int page_size, int window, int keep_first, int cell,
                                 float scale, float softcap, void* out, float* partial, int n_splits, int T_, int nh, int nkv, int dk,
                                 int dv, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
@@ -297,7 +417,7 @@ TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype,
     dim3 grid(T_, nh, n_splits);
     TQ_DISPATCH(act_dtype, TA,
         (tq_launch(grid, BA_WARPS * 32, 0, stream)(bias_attention_kernel<TA>, (const TA*)q, (const TA*)cache, bias, far, sink,
-            positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, (TA*)out, partial,
+            positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, cell, scale, softcap, (TA*)out, partial,
             n_splits, nh, nkv, dk, dv, n_seqs, n_pages)));
     TQ_CHECK_LAUNCH("bias_attention");
     if (n_splits > 1) {
@@ -337,7 +457,7 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ page_table, int table_stride, int page_size, int window,
-                            int keep_first, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int keep_first, int cell, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                             int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -353,7 +473,7 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LPK, part = lane / LPK;           // part: which of the KPI rows of a load
     const int pos = positions[t];
-    const BaSpan span = ba_span(pos, window, keep_first);
+    const BaSpan span = ba_span(pos, ba_window_at(pos, window, cell), cell > 0 ? 0 : keep_first);
     int per = (span.count + n_splits - 1) / n_splits;
     per = (per + GS - 1) / GS * GS;
     const int n0 = split * per, n1 = min(span.count, n0 + per);
@@ -538,7 +658,7 @@ TQ_EXPORT int tq_bias_attention_group_heads(int dk, int dv, int per_kv) { return
 
 TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                                       const int* positions, const int* seq_of_token, const int* page_table,
-                                      int table_stride, int page_size, int window, int keep_first, float scale, float softcap, void* out,
+                                      int table_stride, int page_size, int window, int keep_first, int cell, float scale, float softcap, void* out,
                                       float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
                                       int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
@@ -564,7 +684,7 @@ TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const fl
         }                                                                                                             \
         tq_launch(grid, BA_WARPS * 32, ring_bytes, stream)(bias_attention_group_kernel<DK_, DV_, GC_>, (const __nv_bfloat16*)q,  \
             (const __nv_bfloat16*)cache, bias_t, far, sink, positions, seq_of_token, page_table, table_stride, page_size, \
-            window, keep_first, scale, softcap, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
+            window, keep_first, cell, scale, softcap, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
         done = true;                                                                                                  \
     }
 #define BG_SHAPE(DK_, DV_) BG_CASE(DK_, DV_, 1) BG_CASE(DK_, DV_, 2) BG_CASE(DK_, DV_, 4)
@@ -619,7 +739,7 @@ __global__ void __launch_bounds__(BR_WARPS * 32, 3)
 bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                            const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
-                           const int* __restrict__ page_table, int table_stride, int window, int keep_first,
+                           const int* __restrict__ page_table, int table_stride, int window, int keep_first, int cell,
                            float scale, float softcap, __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -643,9 +763,10 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     const int pos_last = pos0 + n_q - 1;
     const int* table = page_table + (size_t)seq * table_stride;
     // pages to walk: [0, kept) and [first, last]
-    const int first = window > 0 ? max(0, pos0 + 1 - window) / BR_K : 0;
+    // with cells, the block's first query sees back to the start of its cell, the later ones no further
+    const int first = cell > 0 ? (pos0 - pos0 % cell) / BR_K : (window > 0 ? max(0, pos0 + 1 - window) / BR_K : 0);
     const int last = pos_last / BR_K;
-    const int kept = window > 0 ? min((keep_first + BR_K - 1) / BR_K, first) : 0;
+    const int kept = window > 0 && cell == 0 ? min((keep_first + BR_K - 1) / BR_K, first) : 0;
     const int n_tiles = kept + (last - first + 1);
 
     auto load_tile = [&](int i, int stage) {
@@ -727,7 +848,7 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                     const int p = p_base + n * 8 + (lane & 3) * 2 + (c & 1);
                     const int i = (c & 2) ? i_hi : i_lo;
                     const int d = i - p;
-                    const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
+                    const bool see = d >= 0 && (cell > 0 ? p >= i - i % cell : (window == 0 || d < window || p < keep_first));
                     float v = s[n][c] * scale;
                     if (softcap > 0.f) v = softcap * tanhf(v / softcap);
                     if (biased) v += sb[min(max(d - d_min, 0), BR_Q + BR_K - 2)];
@@ -806,7 +927,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ page_table, int table_stride, int page_size, int window,
-                            int keep_first, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int keep_first, int cell, float scale, float softcap, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                             int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
@@ -822,6 +943,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int G = min(16, G_all - chunk * 16);
     const int pos = positions[t];
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+    if (cell > 0) { window = pos % cell + 1; keep_first = 0; }
     const int start = window > 0 ? max(0, pos + 1 - window) : 0;
     const int first = start / BH_K, last = pos / BH_K;
     const int kept = window > 0 ? min((keep_first + BH_K - 1) / BH_K, first) : 0;
@@ -979,7 +1101,7 @@ bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 template <int DK, int DV>
 int launch_bias_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink, const int* positions,
                       const int* seq_of_token, const int* page_table, int table_stride, int page_size, int window,
-                      int keep_first, float scale, float softcap, void* out, float* partial, int n_splits, int T_, int nh, int nkv,
+                      int keep_first, int cell, float scale, float softcap, void* out, float* partial, int n_splits, int T_, int nh, int nkv,
                       int n_seqs, int n_pages, cudaStream_t stream) {
     auto kern = bias_attention_heads_kernel<DK, DV>;
     const int ring = BA_WARPS * 2 * BH_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
@@ -994,14 +1116,14 @@ int launch_bias_heads(const void* q, const void* cache, const float* bias_t, int
     const int chunks = (nh / nkv + 15) / 16;
     dim3 grid(T_, nkv * chunks, n_splits);
     tq_launch(grid, BA_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far, sink,
-        positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, (__nv_bfloat16*)out, partial,
+        positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, cell, scale, softcap, (__nv_bfloat16*)out, partial,
         n_splits, nh, nkv, n_seqs, n_pages);
     return 0;
 }
 
 TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                                       const int* positions, const int* seq_of_token, const int* page_table,
-                                      int table_stride, int page_size, int window, int keep_first, float scale, float softcap, void* out,
+                                      int table_stride, int page_size, int window, int keep_first, int cell, float scale, float softcap, void* out,
                                       float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
                                       int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
@@ -1013,7 +1135,7 @@ TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const fl
     TQ_REQUIRE(n_splits == 1 || partial != nullptr, "bias_attention_heads: %d ranges need scratch for their states", n_splits);
     int rc = -2;
 #define BH_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_heads<DK_, DV_>(q, cache, bias_t, far, sink, positions, \
-        seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, softcap, out, partial, n_splits, T_, nh, nkv,  \
+        seq_of_token, page_table, table_stride, page_size, window, keep_first, cell, scale, softcap, out, partial, n_splits, T_, nh, nkv,  \
         n_seqs, n_pages, stream);
     BH_CASE(32, 32) BH_CASE(32, 64) BH_CASE(32, 128) BH_CASE(64, 32) BH_CASE(64, 64) BH_CASE(64, 128)
     BH_CASE(128, 32) BH_CASE(128, 64) BH_CASE(128, 128)
@@ -1031,7 +1153,7 @@ TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const fl
 template <int DK, int DV>
 int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                      const int* cu_seqlens, const int* seq_start, const int* page_table, int table_stride, int window,
-                     int keep_first, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv, int n_pages,
+                     int keep_first, int cell, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv, int n_pages,
                      cudaStream_t stream) {
     auto kern = bias_attention_runs_kernel<DK, DV>;
     const int smem = 2 * BR_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
@@ -1043,7 +1165,7 @@ int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int 
     }
     dim3 grid(nh, n_seqs, (max_run + BR_Q - 1) / BR_Q);
     tq_launch(grid, BR_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far,
-        sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, scale, softcap, (__nv_bfloat16*)out, nh, nkv, n_pages);
+        sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, cell, scale, softcap, (__nv_bfloat16*)out, nh, nkv, n_pages);
     return 0;
 }
 
@@ -1051,7 +1173,7 @@ int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int 
 TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_dtype, const float* bias_t, int far,
                                      const float* sink, const int* cu_seqlens, const int* seq_start,
                                      const int* page_table, int table_stride, int page_size, int window,
-                                     int keep_first, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv,
+                                     int keep_first, int cell, float scale, float softcap, void* out, int n_seqs, int max_run, int nh, int nkv,
                                      int dk, int dv, int n_pages, cudaStream_t stream) {
     if (n_seqs == 0 || max_run == 0) return 0;
     TQ_REQUIRE(act_dtype == TQ_BF16, "bias_attention_runs: bfloat16 only");
@@ -1061,7 +1183,7 @@ TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_d
     TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_runs: negative window, kept positions or distance");
     int rc = -2;
 #define BR_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_runs<DK_, DV_>(q, cache, bias_t, far, sink, cu_seqlens, \
-        seq_start, page_table, table_stride, window, keep_first, scale, softcap, out, n_seqs, max_run, nh, nkv, n_pages, stream);
+        seq_start, page_table, table_stride, window, keep_first, cell, scale, softcap, out, n_seqs, max_run, nh, nkv, n_pages, stream);
     BR_CASE(32, 32) BR_CASE(32, 64) BR_CASE(32, 128) BR_CASE(64, 32) BR_CASE(64, 64) BR_CASE(64, 128)
     BR_CASE(128, 32) BR_CASE(128, 64) BR_CASE(128, 128)
 #undef BR_CASE

@@ -845,3 +845,159 @@ TQ_EXPORT int tq_scale_bias_cols(float* x, const float* bias, float scale, int T
     TQ_CHECK_LAUNCH("scale_bias_cols");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Dynamic tanh, a norm without statistics: out[r, i] = tanh(alpha * v[i]) * w[i] + b[i] with v the row rows[r] of x
+// (all rows in order if rows is null), or x + scale * y where y is given (x then takes the sum, as in rmsnorm).
+// With `shift`, the output is mixed with the token before: out = h + (h' - h) * shift[i], h' being the norm's
+// unshifted output for the previous token of the sequence: the row above inside a run of new tokens, the sequence's
+// kept row (state, fp32 [slots][H] with a row stride) for a run's first token, which is zero at a sequence's start.
+// keep != 0 (steps in which every sequence brings one token): the token's own unshifted output becomes the kept row
+// in the same pass; otherwise tq_dyt_keep_last does that in a launch of its own, since other blocks still read the
+// old rows.  Shift and y exclude each other (the row above must not change under the kernel).
+// ---------------------------------------------------------------------------------------
+template <typename TY, typename TW, typename TO>
+__global__ void dyt_kernel(float* __restrict__ x, const TY* __restrict__ y, float scale, const int* __restrict__ rows, float alpha,
+                           const TW* __restrict__ w, const TW* __restrict__ b, TO* __restrict__ out, int H,
+                           const TW* __restrict__ shift, float* __restrict__ state, long long slot_stride,
+                           const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
+                           const int* __restrict__ slots, int keep) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* xr = x + src * H;
+    const float* above = nullptr;      // the row of the token before, inside this step
+    float* kept = nullptr;             // the sequence's kept row
+    if (shift != nullptr) {
+        const int s = seq_of_token[src];
+        kept = state + (size_t)slots[s] * slot_stride;
+        if ((int)src > cu_seqlens[s]) above = xr - H;
+    }
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
+        float v = xr[i];
+        if (y != nullptr) {
+            v += scale * tq_to_float(y[src * H + i]);
+            if (rows == nullptr) xr[i] = v;
+        }
+        const float wi = tq_to_float(w[i]), bi = tq_to_float(b[i]);
+        float h = tanhf(alpha * v) * wi + bi;
+        if (shift != nullptr) {
+            const float before = above ? tanhf(alpha * above[i]) * wi + bi : kept[i];
+            if (keep) kept[i] = h;
+            h += (before - h) * tq_to_float(shift[i]);
+        }
+        out[r * H + i] = tq_from_float<TO>(h);
+    }
+}
+
+// kept row of every sequence <- the unshifted norm of its last token of this step; grid (sequences, column chunks)
+template <typename TW>
+__global__ void dyt_keep_last_kernel(const float* __restrict__ x, float alpha, const TW* __restrict__ w, const TW* __restrict__ b,
+                                     int H, float* __restrict__ state, long long slot_stride,
+                                     const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int s = blockIdx.x;
+    const int last = cu_seqlens[s + 1] - 1;
+    if (last < cu_seqlens[s]) return;
+    const float* xr = x + (size_t)last * H;
+    float* kept = state + (size_t)slots[s] * slot_stride;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x)
+        kept[i] = tanhf(alpha * xr[i]) * tq_to_float(w[i]) + tq_to_float(b[i]);
+}
+
+TQ_EXPORT int tq_dyt(float* x, const void* y, int y_dtype, float scale, const int* rows, float alpha, const void* w,
+                     const void* b, int w_dtype, void* out, int out_dtype, int R, int H, const void* shift, float* state,
+                     long long slot_stride, const int* seq_of_token, const int* cu_seqlens, const int* slots, int n_seqs,
+                     int keep, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(H >= 1, "dyt: rows of %d elements", H);
+    TQ_REQUIRE(shift == nullptr || (y == nullptr && rows == nullptr && state != nullptr && seq_of_token != nullptr &&
+                                    cu_seqlens != nullptr && slots != nullptr),
+               "dyt: the shift wants whole steps, the sequences' kept rows and no sum on the way");
+    if (y == nullptr) y_dtype = TQ_F32;
+    const int threads = H >= 1024 ? 256 : 128;
+    dim3 grid(R, (H + 8 * threads - 1) / (8 * threads));
+    TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch(grid, threads, 0, stream)(dyt_kernel<TY, TW, TO>, x, (const TY*)y, scale, rows, alpha, (const TW*)w, (const TW*)b,
+            (TO*)out, H, (const TW*)shift, state, slot_stride, seq_of_token, cu_seqlens, slots, keep)))));
+    TQ_CHECK_LAUNCH("dyt");
+    if (shift != nullptr && !keep) {
+        TQ_DISPATCH(w_dtype, TW,
+            (tq_launch(dim3(n_seqs, grid.y), threads, 0, stream)(dyt_keep_last_kernel<TW>, (const float*)x, alpha, (const TW*)w, (const TW*)b, H,
+                state, slot_stride, cu_seqlens, slots)));
+        TQ_CHECK_LAUNCH("dyt_keep_last");
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// A weighted sum over the depth of a model: hist holds the stream as every layer so far left it, [n][N] fp32.
+// Entry `at` is written first as x + scale * (f + bias) (f: a sub-layer's output still to be added, rows of H
+// elements; bias [H]; both may be null), then out = sum over j <= at of weights[j] * hist[j].  x and out may be
+// the same tensor.
+// ---------------------------------------------------------------------------------------
+template <typename TY, typename TW>
+__global__ void depth_mix_kernel(float* hist, int at, size_t N, const float* x, const TY* __restrict__ f,
+                                 const TW* __restrict__ bias, int H, float scale, const float* __restrict__ weights, float* out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < N; i += stride) {
+        float v = x[i];
+        if (f != nullptr) v += scale * (tq_to_float(f[i]) + (bias ? tq_to_float(bias[i % H]) : 0.f));
+        hist[(size_t)at * N + i] = v;
+        float acc = weights[at] * v;
+        for (int j = at - 1; j >= 0; --j) acc += weights[j] * hist[(size_t)j * N + i];
+        out[i] = acc;
+    }
+}
+
+TQ_EXPORT int tq_depth_mix(float* hist, int at, long long N, const float* x, const void* f, int f_dtype, const void* bias,
+                           int bias_dtype, int H, float scale, const float* weights, float* out, cudaStream_t stream) {
+    if (N == 0) return 0;
+    TQ_REQUIRE(at >= 0 && H >= 1 && N % H == 0, "depth_mix: entry %d, rows of %d in %lld elements", at, H, N);
+    if (f == nullptr) f_dtype = TQ_F32;
+    if (bias == nullptr) bias_dtype = TQ_F32;
+    const int threads = 256;
+    long long blocks = (N + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TQ_DISPATCH(f_dtype, TY, TQ_DISPATCH(bias_dtype, TW,
+        (tq_launch((int)blocks, threads, 0, stream)(depth_mix_kernel<TY, TW>, hist, at, (size_t)N, x, (const TY*)f, (const TW*)bias, H,
+            scale, weights, out))));
+    TQ_CHECK_LAUNCH("depth_mix");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, i] = act(in[t, i] + bias[i]) for fp32 rows: a projection's bias and the activation behind it in one pass
+// (act as in tq_map: 0 identity, 1 the square of relu).
+// ---------------------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void bias_map_kernel(const float* __restrict__ in, const TW* __restrict__ bias, TO* __restrict__ out, size_t n, int N, int act) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        float v = in[i] + tq_to_float(bias[i % N]);
+        if (act == 1) { v = fmaxf(v, 0.f); v = v * v; }
+        out[i] = tq_from_float<TO>(v);
+    }
+}
+
+TQ_EXPORT int tq_bias_map(const float* in, const void* bias, int bias_dtype, void* out, int out_dtype, int T_, int N, int act,
+                          cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(N >= 1 && (act == 0 || act == 1), "bias_map: rows of %d, function %d", N, act);
+    const long long n = (long long)T_ * N;
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TQ_DISPATCH(bias_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch((int)blocks, threads, 0, stream)(bias_map_kernel<TW, TO>, in, (const TW*)bias, (TO*)out, (size_t)n, N, act))));
+    TQ_CHECK_LAUNCH("bias_map");
+    return 0;
+}

@@ -11,6 +11,7 @@
 //   conv_state_update  the kept inputs after the step (a launch of its own: conv_silu reads the old ones)
 //   ssm_scan           the recurrence over each sequence's run of new tokens, a warp per four columns of the state
 //   gated_group_norm   y * silu(z), RMS norm in equal groups, weight
+//   delta_scan         the delta rule with a decay per key channel (its own header below)
 #include <type_traits>
 
 #include "common.cuh"
@@ -325,12 +326,13 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
 // out[t, g-th part] = rms(y[t, part] * silu(z[t, part])) * w[part]: the gate first, then the norm of each of the
 // `norm_groups` equal parts by its own root mean square.  z is `inner` elements of the projection's row from z_off.
 // gate_after: the norm first, then the gate: rms(y[t, part]) * w[part] * silu(z[t, part]).  w may be null (no weight).
+// gate_kind 1: sigmoid(z) where silu(z) stands above.
 // ---------------------------------------------------------------------------------------
 #define GGN_KEEP 8
 template <typename TW, typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
                                         const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, float eps,
-                                        int gate_after) {
+                                        int gate_after, int gate_kind) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
@@ -338,7 +340,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     const int base = blockIdx.y * gs;
     const float* yr = y + t * inner + base;
     const float* zr = proj + t * P + z_off + base;
-    auto silu = [](float z) { return z / (1.0f + expf(-z)); };
+    auto silu = [gate_kind](float z) { return (gate_kind ? 1.0f : z) / (1.0f + expf(-z)); };     // or the sigmoid alone
     // a thread's (gated) values stay in registers between the sum of squares and the output (up to GGN_KEEP of them;
     // longer parts compute the rest again)
     float keep[GGN_KEEP];
@@ -377,7 +379,7 @@ template <typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
                              const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, int n_groups, float eps,
-                             int gate_after) {
+                             int gate_after, int gate_kind) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const size_t t = blockIdx.x;
@@ -386,7 +388,7 @@ gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restric
     const int base = g * gs;
     const float* yr = y + t * inner + base;
     const float* zr = proj + t * P + z_off + base;
-    auto silu = [](float z) { return z / (1.0f + expf(-z)); };
+    auto silu = [gate_kind](float z) { return (gate_kind ? 1.0f : z) / (1.0f + expf(-z)); };     // or the sigmoid alone
     float keep[GGN_KEEP], gate[GGN_KEEP];
     float ss = 0.f;
 #pragma unroll
@@ -415,7 +417,7 @@ gated_group_norm_warp_kernel(const float* __restrict__ y, const float* __restric
 
 TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int z_off, const void* w, int w_dtype,
                                   void* out, int out_dtype, int T_, int inner, int norm_groups, float eps, int gate_after,
-                                  cudaStream_t stream) {
+                                  int gate_kind, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(inner >= 1 && norm_groups >= 1 && inner % norm_groups == 0 && norm_groups <= 65535,
                "gated_group_norm: %d elements in %d groups", inner, norm_groups);
@@ -427,13 +429,13 @@ TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int 
     if (gs <= 32 * GGN_KEEP && norm_groups >= 4) {
         TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
             (tq_launch(dim3(T_, (norm_groups + 3) / 4), 128, 0, stream)(gated_group_norm_warp_kernel<TW, TO>, y, proj, P, z_off,
-                (const TW*)w, (TO*)out, inner, gs, norm_groups, eps, gate_after))));
+                (const TW*)w, (TO*)out, inner, gs, norm_groups, eps, gate_after, gate_kind))));
         TQ_CHECK_LAUNCH("gated_group_norm");
         return 0;
     }
     TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(grid, threads, 0, stream)(gated_group_norm_kernel<TW, TO>, y, proj, P, z_off, (const TW*)w, (TO*)out,
-                                             inner, gs, eps, gate_after))));
+                                             inner, gs, eps, gate_after, gate_kind))));
     TQ_CHECK_LAUNCH("gated_group_norm");
     return 0;
 }
@@ -632,5 +634,141 @@ TQ_EXPORT int tq_retention_step(const float* proj, int P, int q_off, int k_off, 
         (tq_launch(dim3(T_, heads), threads, (size_t)dv * sizeof(float), stream)(retention_step_kernel<TO>, proj, P, q_off, k_off, v_off,
             g_off, freq, rot_dims, halves, k_scale, positions, state, slot_stride, slots, decay, (TO*)out, heads, dk, dv, eps)));
     TQ_CHECK_LAUNCH("retention_step");
+    return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// The delta rule with a decay per key channel.  Per head a with state S [dk, dv] (fp32, one per sequence, carried from
+// step to step), for every token of a sequence's run in order:
+//   S   <- diag(g) S            g = exp(-exp(A_log_a) * softplus(raw + dt_bias)), one decay per key channel
+//   u    = beta * (v - S^T k)   beta = sigmoid(raw beta), k the unit vector of the head's key
+//   S   <- S + k u^T
+//   o    = S^T q                q the unit vector of the head's query times q_scale; it sees the token's own write
+// unit(x) = x / sqrt(sum(x^2) + unit_eps).  q and k (kv_heads x dk, head a reads a / (heads / kv_heads)) and v
+// (heads x dv) come from xqkv (fp32 rows, the output of conv_silu); raw beta from a projection's fp32 rows; the raw
+// decays from fp32 rows of heads x dk.  Everything is fp32.
+// Grid (sequence, head, ceil(dv / 16)), four warps: a warp owns four columns of S (kept column by column, [dv][dk]),
+// eight lanes a column, lane `sub` of them the rows sub, sub + 8, ... in registers for the whole run.  The run is
+// walked in chunks of `tc` tokens whose unit vectors, decays, values and betas the block prepares in shared memory
+// (a warp per token; rows beyond dk as zeros, so the state's padding rows stay zero and need no test).
+// ---------------------------------------------------------------------------------------
+#define DELTA_COLS 16
+template <int RPL>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ xqkv, int C, int q_off, int k_off, int v_off,
+                  const float* __restrict__ proj, int P, int b_off, const float* __restrict__ a_raw, int A, int a_off,
+                  const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ state,
+                  long long slot_stride, float* __restrict__ y, int heads, int kv_heads, int dk, int dv, float unit_eps,
+                  float q_scale, int tc, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int DKP = RPL * 8;
+    extern __shared__ float delta_smem[];
+    float* sk = delta_smem;                    // [tc][DKP]
+    float* sq = sk + (size_t)tc * DKP;
+    float* sg = sq + (size_t)tc * DKP;
+    float* sv = sg + (size_t)tc * DKP;         // [tc][DELTA_COLS]
+    float* sb = sv + (size_t)tc * DELTA_COLS;  // [tc]
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
+    const int lc = warp * 4 + (lane >> 3), col = c0 + lc;
+    const bool live = col < dv;
+    const int g = h / (heads / kv_heads);
+    const int t0 = cu_seqlens[s], n = cu_seqlens[s + 1] - t0;
+    float* Sp = state + (size_t)slots[s] * slot_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
+    float S[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int row = sub + 8 * r;
+        S[r] = live && row < dk ? Sp[row] : 0.f;
+    }
+    const float rate = expf(a_log[h]);
+    for (int base = 0; base < n; base += tc) {
+        const int nt = min(tc, n - base);
+        for (int i = warp; i < nt; i += 4) {
+            const size_t t = (size_t)t0 + base + i;
+            const float* kr = xqkv + t * C + k_off + (size_t)g * dk;
+            const float* qr = xqkv + t * C + q_off + (size_t)g * dk;
+            const float* ar = a_raw + t * A + a_off + (size_t)h * dk;
+            float ssk = 0.f, ssq = 0.f;
+            for (int e = lane; e < dk; e += 32) { ssk += kr[e] * kr[e]; ssq += qr[e] * qr[e]; }
+            const float rk = 1.0f / sqrtf(tq_warp_sum(ssk) + unit_eps);
+            const float rq = q_scale / sqrtf(tq_warp_sum(ssq) + unit_eps);
+            for (int e = lane; e < DKP; e += 32) {
+                float kv = 0.f, qv = 0.f, gv = 0.f;
+                if (e < dk) {
+                    kv = kr[e] * rk;
+                    qv = qr[e] * rq;
+                    const float z = ar[e] + dt_bias[(size_t)h * dk + e];
+                    const float sp = z > 20.f ? z : log1pf(expf(z));
+                    gv = expf(-rate * sp);
+                }
+                sk[i * DKP + e] = kv; sq[i * DKP + e] = qv; sg[i * DKP + e] = gv;
+            }
+            if (lane < DELTA_COLS) sv[i * DELTA_COLS + lane] = c0 + lane < dv ? xqkv[t * C + v_off + (size_t)h * dv + c0 + lane] : 0.f;
+            if (lane == 0) sb[i] = 1.0f / (1.0f + expf(-proj[t * P + b_off + h]));
+        }
+        __syncthreads();
+        for (int i = 0; i < nt; ++i) {
+            const float* ki = sk + i * DKP + sub;
+            const float* qi = sq + i * DKP + sub;
+            const float* gi = sg + i * DKP + sub;
+            float pred = 0.f;
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) {
+                S[r] *= gi[8 * r];
+                pred += S[r] * ki[8 * r];
+            }
+            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 4);
+            const float u = sb[i] * (sv[i * DELTA_COLS + lc] - pred);
+            float o = 0.f;
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) {
+                S[r] += ki[8 * r] * u;
+                o += S[r] * qi[8 * r];
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (sub == 0 && live) y[((size_t)t0 + base + i) * heads * dv + (size_t)h * dv + col] = o;
+        }
+        __syncthreads();
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RPL; ++r) {
+            const int row = sub + 8 * r;
+            if (row < dk) Sp[row] = S[r];
+        }
+    }
+}
+
+// xqkv fp32 [T, C]; proj fp32 [T, P] (raw beta of head a at b_off + a); a_raw fp32 [T, A] (raw decays of head a from
+// a_off + a * dk); dt_bias fp32 [heads * dk]; a_log fp32 [heads]; state fp32 rows of [heads][dv][dk] at slots[s] *
+// slot_stride; y fp32 [T, heads * dv].
+TQ_EXPORT int tq_delta_scan(const float* xqkv, int C, int q_off, int k_off, int v_off, const float* proj, int P, int b_off,
+                            const float* a_raw, int A, int a_off, const float* dt_bias, const float* a_log, float* state,
+                            long long slot_stride, float* y, int n_seqs, int heads, int kv_heads, int dk, int dv,
+                            float unit_eps, float q_scale, const int* cu_seqlens, const int* slots, cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && kv_heads >= 1 && heads % kv_heads == 0 && heads <= 65535, "delta_scan: %d heads on %d query/key heads", heads, kv_heads);
+    TQ_REQUIRE(dk >= 1 && dk <= SSM_MAX_STATE && dv >= 1, "delta_scan: keys of %d elements (1..%d), values of %d", dk, SSM_MAX_STATE, dv);
+    TQ_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + kv_heads * dk <= C && k_off + kv_heads * dk <= C && v_off + heads * dv <= C,
+               "delta_scan: queries, keys or values lie outside rows of %d", C);
+    TQ_REQUIRE(b_off >= 0 && b_off + heads <= P && a_off >= 0 && a_off + heads * dk <= A, "delta_scan: betas or decays lie outside their rows");
+    const int rpl = dk <= 64 ? 8 : (dk <= 128 ? 16 : 32);
+    const int tc = rpl <= 16 ? 16 : 8;
+    const size_t smem = ((size_t)3 * rpl * 8 + DELTA_COLS + 1) * tc * sizeof(float);
+    dim3 grid(n_seqs, heads, (dv + DELTA_COLS - 1) / DELTA_COLS);
+    TQ_REQUIRE(grid.z <= 65535, "delta_scan: values of %d elements exceed the grid limit", dv);
+#define DELTA_LAUNCH(R)                                                                                                 \
+    tq_launch(grid, 128, smem, stream)(delta_scan_kernel<R>, xqkv, C, q_off, k_off, v_off, proj, P, b_off, a_raw, A, a_off, \
+        dt_bias, a_log, state, slot_stride, y, heads, kv_heads, dk, dv, unit_eps, q_scale, tc, cu_seqlens, slots)
+    if (rpl == 8) DELTA_LAUNCH(8); else if (rpl == 16) DELTA_LAUNCH(16); else DELTA_LAUNCH(32);
+#undef DELTA_LAUNCH
+    TQ_CHECK_LAUNCH("delta_scan");
     return 0;
 }

@@ -261,3 +261,64 @@ def ctypes_ptr(t: torch.Tensor):
     if not t.is_cuda:
         raise KernelError("kernels take CUDA tensors; there is no CPU path")
     return ctypes.c_void_p(t.data_ptr())
+
+
+def dyt(x: torch.Tensor, alpha: float, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
+        add: Optional[torch.Tensor] = None, add_scale: float = 1.0, rows: Optional[torch.Tensor] = None,
+        shift: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, seq_of_token: Optional[torch.Tensor] = None,
+        cu_seqlens: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None, single_tokens: bool = False) -> torch.Tensor:
+    """out = tanh(alpha * v) * weight + bias for the rows v of x float32 [T, H] (`rows`: those rows only), or of
+    x + add_scale * add, which x then holds (without `rows`).  shift [H]: the output h_t becomes
+    h_t + (h_(t-1) - h_t) * shift, h_(t-1) the unshifted output of the sequence's token before: the row above inside a
+    run, else the sequence's kept row state[slots[s]] (float32 [max_slots, H], rows may be strided; zero at a
+    sequence's start), which afterwards holds the run's last unshifted output.  single_tokens: every sequence brings
+    one token (the kept rows are renewed in the same launch)."""
+    want_f32(x, "the residual stream")
+    R = x.shape[0] if rows is None else rows.shape[0]
+    H = x.shape[1]
+    if weight.dtype != bias.dtype or (shift is not None and shift.dtype != weight.dtype):
+        raise KernelError("dyt: weight, bias and shift must share a dtype")
+    n_seqs = 0
+    if shift is not None:
+        if add is not None or rows is not None or state is None:
+            raise KernelError("dyt: the shift wants whole steps, the sequences' kept rows and no sum on the way")
+        want_f32(state, "the kept rows")
+        if state.shape[1] != H or state.stride(1) != 1:
+            raise KernelError("dyt: kept rows of the stream's width")
+        n_seqs = cu_seqlens.shape[0] - 1
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_dyt(ptr(x), ptr(add), c_int(code(add.dtype) if add is not None else 0), c_float(add_scale), ptr(rows),
+                           c_float(alpha), ptr(weight), ptr(bias), c_int(code(weight.dtype)), ptr(out), c_int(code(out.dtype)),
+                           c_int(R), c_int(H), ptr(shift), ctypes_ptr(state) if state is not None else None,
+                           c_longlong(state.stride(0) if state is not None else 0), ptr(seq_of_token), ptr(cu_seqlens),
+                           ptr(slots), c_int(n_seqs), c_int(1 if single_tokens else 0), stream()),
+          kernels=2 if shift is not None and not single_tokens else 1)
+    return out
+
+
+def depth_mix(hist: torch.Tensor, at: int, x: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+              add: Optional[torch.Tensor] = None, add_scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """hist float32 [n, T, H]: hist[at] = x + add_scale * (add + bias), then out = sum over j <= at of weights[j] *
+    hist[j].  weights float32 [>= at + 1]; x and out float32 [T, H] (they may be one tensor); add [T, H], bias [H]."""
+    for t, what in ((hist, "the kept streams"), (x, "the stream"), (weights, "the weights"), (out, "the output")):
+        want_f32(t, what)
+    if hist.shape[1:] != x.shape or out.shape != x.shape or not 0 <= at < hist.shape[0] or weights.numel() <= at:
+        raise KernelError("depth_mix: kept streams, stream, output and weights do not fit together")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_depth_mix(ptr(hist), c_int(at), c_longlong(x.numel()), ptr(x), ptr(add),
+                                 c_int(code(add.dtype) if add is not None else 0), ptr(bias),
+                                 c_int(code(bias.dtype) if bias is not None else 0), c_int(x.shape[1]), c_float(add_scale),
+                                 ptr(weights), ptr(out), stream()))
+    return out
+
+
+def bias_map(src: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, function: int = MAP_COPY) -> torch.Tensor:
+    """out[t, i] = f(src[t, i] + bias[i]) for float32 rows src [T, N], rounded to out's dtype."""
+    want_f32(src, "the rows")
+    T, N = src.shape
+    if bias.numel() != N or out.shape != src.shape:
+        raise KernelError("bias_map: one bias per column, an output of the input's shape")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_bias_map(ptr(src), ptr(bias), c_int(code(bias.dtype)), ptr(out), c_int(code(out.dtype)), c_int(T),
+                                c_int(N), c_int(function), stream()))
+    return out

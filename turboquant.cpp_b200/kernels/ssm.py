@@ -104,10 +104,10 @@ def retention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, ou
 
 
 def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: Optional[torch.Tensor], norm_groups: int,
-                     eps: float, out: torch.Tensor, gate_after: bool = False) -> torch.Tensor:
+                     eps: float, out: torch.Tensor, gate_after: bool = False, sigmoid_gate: bool = False) -> torch.Tensor:
     """out = rms_in_groups(y * silu(z)) * weight with z = proj[:, z_off:z_off+inner]: the gate first, then each of
     the norm_groups equal parts of a row divided by its own root mean square.  gate_after: the norm first, then the
-    gate: rms_in_groups(y) * weight * silu(z).  weight None: no weight."""
+    gate: rms_in_groups(y) * weight * silu(z).  weight None: no weight.  sigmoid_gate: sigmoid(z) where silu(z) stands."""
     want_f32(y, "the recurrence's output")
     want_f32(proj, "the projection")
     T, inner = y.shape
@@ -115,7 +115,7 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: Op
     check(_LIB, lib.tq_gated_group_norm(ptr(y), ptr(proj), c_int(proj.shape[1]), c_int(z_off), ptr(weight),
                                         c_int(code(weight.dtype) if weight is not None else 0), ptr(out),
                                         c_int(code(out.dtype)), c_int(T), c_int(inner), c_int(norm_groups), c_float(eps),
-                                        c_int(1 if gate_after else 0), stream()))
+                                        c_int(1 if gate_after else 0), c_int(1 if sigmoid_gate else 0), stream()))
     return out
 
 
@@ -165,3 +165,31 @@ def retention_step(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off
                                       ctypes_ptr(state), c_longlong(state.stride(0)), ptr(slots), ptr(decay), ptr(out),
                                       c_int(code(out.dtype)), c_int(T), c_int(heads), c_int(dk), c_int(dv), c_float(eps), stream()))
     return out
+
+
+def delta_scan(xqkv: torch.Tensor, q_off: int, k_off: int, v_off: int, proj: torch.Tensor, b_off: int, a_raw: torch.Tensor,
+               a_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, y: torch.Tensor, heads: int,
+               kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor) -> torch.Tensor:
+    """The delta rule with a decay per key channel over every sequence's run of new tokens:
+    S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; y = S^T q, with k and q made unit vectors
+    (x / sqrt(sum(x^2) + unit_eps), q times q_scale), beta = sigmoid(proj[:, b_off + a]) and
+    g = exp(-exp(a_log[a]) * softplus(a_raw[:, a_off + a*dk : ...] + dt_bias[a])).  xqkv float32 [T, C] holds q, k
+    (kv_heads x dk) and v (heads x dv) from the given columns; state float32 [max_slots, heads, dv, dk] (a head's
+    state column by column; rows may be strided); y float32 [T, heads*dv]."""
+    for t, what in ((xqkv, "q, k and v"), (proj, "the projection"), (a_raw, "the raw decays"), (dt_bias, "the decays' bias"),
+                    (a_log, "the decay rates"), (state, "the state"), (y, "the output")):
+        want_f32(t, what)
+    want_int32(cu_seqlens, "the sequences' bounds")
+    want_int32(slots, "slots")
+    if tuple(state.shape[1:]) != (heads, dv, dk) or not state[0].is_contiguous():
+        raise KernelError("delta_scan: the state must be [slots, heads, vdim, dim] with dense rows")
+    if dt_bias.numel() != heads * dk or a_log.numel() != heads or y.shape != (xqkv.shape[0], heads * dv):
+        raise KernelError("delta_scan: one decay bias per head and key channel, one rate per head, an output of heads*dv")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_delta_scan(ptr(xqkv), c_int(xqkv.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), ptr(proj),
+                                  c_int(proj.shape[1]), c_int(b_off), ptr(a_raw), c_int(a_raw.shape[1]), c_int(a_off),
+                                  ptr(dt_bias), ptr(a_log), ctypes_ptr(state), c_longlong(state.stride(0)), ptr(y),
+                                  c_int(cu_seqlens.shape[0] - 1), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+                                  c_float(unit_eps), c_float(q_scale), ptr(cu_seqlens), ptr(slots), stream()))
+    return y

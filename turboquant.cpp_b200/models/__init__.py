@@ -4,3 +4,4 @@ from .qwen2_moe import Qwen2MoeModel
 from .nuforax import NuforaxModel
 from .lumevik import LumevikModel
 from .sisepel import SisepelModel
+from .tasadra import TasadraModel

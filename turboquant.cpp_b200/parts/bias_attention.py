@@ -49,6 +49,35 @@ def distance_buckets(rows: int, far: int) -> List[int]:
     return out
 
 
+def paged_attention(q: torch.Tensor, cache: LayerCache, ctx: StepContext, heads: int, kv_heads: int, dim: int, vdim: int,
+                    scale: float, window: int = 0, keep_first: int = 0, bias: Optional[torch.Tensor] = None,
+                    bias_t: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                    cell: int = 0, runs_min: int = 16) -> torch.Tensor:
+    """Softmax attention of the step's queries q [T, heads, dim] over the rows [k | v] of a paged cache, [T, heads *
+    vdim] in the activation dtype: the kernel for runs of new tokens where the step has a run of runs_min tokens and
+    the shape is one it is built for, else one of the token forms with the visible keys cut into ranges.  The mask
+    is a window (with a sequence's first positions kept) or, with cell > 0, the query's own cell of positions."""
+    T, act, dev = q.shape[0], ctx.act_dtype, q.device
+    o = torch.empty((T, heads * vdim), dtype=act, device=dev)
+    if ctx.max_q_len >= runs_min and KB.runs_usable(act, dim, vdim, cache.page_size):
+        return KB.attention_runs(q, cache.kv, bias_t, sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table, cache.page_size,
+                                 window, keep_first, scale, o, ctx.n_seqs, ctx.max_q_len, heads, kv_heads, dim, vdim,
+                                 softcap=softcap, cell=cell)
+    if cell:
+        longest = min(cell, ctx.max_kv_len)
+    else:
+        longest = min(window + keep_first, ctx.max_kv_len) if window else ctx.max_kv_len
+    per_kv = heads // kv_heads
+    gc = KB.group_heads(act, dim, vdim, per_kv)
+    blocks = kv_heads * -(-per_kv // gc) if gc else heads
+    unit = 8
+    if KB.heads_form(act, dim, vdim, per_kv, cache.page_size):
+        blocks, unit = kv_heads * -(-per_kv // 16), 16
+    return KB.attention(q, cache.kv, bias, sink, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
+                        window, keep_first, scale, o, heads, kv_heads, dim, vdim,
+                        n_splits=KB.splits_for(T, blocks, longest, dev, unit), bias_t=bias_t, softcap=softcap, cell=cell)
+
+
 class BiasedWindowAttentionMixer(Mixer):
     RUNS_MIN = 16             # steps whose longest run of new tokens is at least this take the kernel for runs
 
@@ -166,23 +195,9 @@ class BiasedWindowAttentionMixer(Mixer):
         else:
             KB.kv_write(qkv, q, cache.kv if cache.writes else None, keep, other, self.mix, ctx.positions, ctx.seq_of_token,
                         cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
-        o = torch.empty((T, self.heads * self.vdim), dtype=act, device=dev)
-        if ctx.max_q_len >= self.RUNS_MIN and KB.runs_usable(act, self.dim, self.vdim, cache.page_size):
-            KB.attention_runs(q, cache.kv, self.bias_t, self.sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table,
-                              cache.page_size, self.window, self.keep_first, self.scale, o, ctx.n_seqs, ctx.max_q_len,
-                              self.heads, self.kv_heads, self.dim, self.vdim, softcap=self.softcap)
-        else:
-            longest = min(self.window + self.keep_first, ctx.max_kv_len) if self.window else ctx.max_kv_len
-            per_kv = self.heads // self.kv_heads
-            gc = KB.group_heads(act, self.dim, self.vdim, per_kv)
-            blocks = self.kv_heads * -(-per_kv // gc) if gc else self.heads
-            unit = 8
-            if KB.heads_form(act, self.dim, self.vdim, per_kv, cache.page_size):
-                blocks, unit = self.kv_heads * -(-per_kv // 16), 16
-            KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
-                         cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
-                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev, unit), bias_t=self.bias_t,
-                         softcap=self.softcap)
+        o = paged_attention(q, cache, ctx, self.heads, self.kv_heads, self.dim, self.vdim, self.scale, window=self.window,
+                            keep_first=self.keep_first, bias=self.bias, bias_t=self.bias_t, sink=self.sink,
+                            softcap=self.softcap, runs_min=self.RUNS_MIN)
         if KG.pays(o, self.w_o):                   # a few tokens: the output projection as a stream of its weights
             return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
         return linear(o, self.w_o, out_dtype=torch.float32)

@@ -205,3 +205,111 @@ class SandwichBlock(Block):
         if xn is not None and out_norm is not None:
             ctx.carry[NORMED_STREAM] = xn
         return x, None
+
+
+KEPT_STREAMS = "kept_streams"       # StepContext.carry: the stream as the embedding and every layer so far left it
+
+
+class DepthMixBlock(Block):
+    """A pre-norm block with a factor on its sums, a token shift ahead of the mixer and a weighted sum over depth:
+
+        h = shift(norm1(x));  y = x + r * mixer(h);  X = y + r * feed_forward(norm2(y))      (the second sum only with a
+                                                                                              feed-forward)
+        shift(h)_t = h_t + (h_(t-1) - h_t) * s       s: the tensor `shift_name`; h_(t-1) unshifted, zero before a sequence's
+                                                     first token; a sequence keeps its last h (None: no shift)
+        x <- sum_j depth[j] * X_j                    over the embedding's output X_0 and the results X_1 .. of all blocks
+                                                     up to this one (`depth_name`: weights [index + 2]; None: x <- X)
+
+    index: how many blocks of this kind ran before this one in the model (the blocks share the kept streams through
+    the step's carry; `depth_total` of them, the embedding's output included, are kept).  The norms are DynamicTanh
+    (`shifted`, `add_forward(scale=)`).  The stream stays float32.  The sequence's kept row of the shift lies ahead of
+    the mixer's own state in the block's state row."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn: Optional[FeedForward] = None,
+                 hidden: int = 0, residual_mult: float = 1.0, shift_name: Optional[str] = None,
+                 depth_name: Optional[str] = None, index: int = 0, depth_total: int = 0):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        if hidden < 1 or index < 0 or (depth_name is not None and depth_total < index + 2):
+            raise ValueError(f"block: width {hidden}, place {index} of {depth_total} kept streams")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.hidden, self.mult, self.shift_name, self.depth_name = int(hidden), float(residual_mult), shift_name, depth_name
+        self.index, self.depth_total = int(index), int(depth_total)
+        self.shift: Optional[torch.Tensor] = None
+        self.depth: Optional[torch.Tensor] = None
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def cache_need(self) -> Optional[KVNeed]:
+        return self.mixer.cache_need()
+
+    def _own_state(self) -> int:
+        return self.hidden if self.shift_name is not None else 0
+
+    def state_need(self) -> Optional[StateNeed]:
+        inner = self.mixer.state_need()
+        if inner is not None and (inner.dtype != torch.float32 or len(inner.shape) != 1):
+            raise ValueError("block: a mixer behind a token shift keeps its state as one float32 row")
+        size = self._own_state() + (inner.shape[0] if inner is not None else 0)
+        return StateNeed((size,), torch.float32) if size else None
+
+    def capturable(self) -> bool:
+        return self.mixer.capturable() and (self.ffn is None or self.ffn.capturable())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self.parts() for s in p.weight_specs()]
+        if self.shift_name is not None:
+            specs.append(WeightSpec(self.shift_name, (self.hidden,)))
+        if self.depth_name is not None:
+            specs.append(WeightSpec(self.depth_name, (self.index + 2,), init="one_plus_normal"))
+        return specs
+
+    def bind(self, store: WeightStore) -> None:
+        for p in self.parts():
+            p.bind(store)
+        if self.shift_name is not None:
+            self.shift = store.get(self.shift_name)
+        if self.depth_name is not None:
+            self.depth = store.get(self.depth_name).float().contiguous()
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"] + [k for p in self.parts() for k in p.kernels()]
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if pending is not None:                      # a block of another kind ran before and left its sum open
+            K.residual_add(x, pending)
+        hist = None
+        if self.depth is not None:
+            hist = ctx.carry.get(KEPT_STREAMS)
+            if hist is None:
+                hist = ctx.carry[KEPT_STREAMS] = torch.empty((self.depth_total,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+                hist[0].copy_(x)
+        own = self._own_state()
+        if own:
+            h = self.mixer_norm.shifted(x, ctx.act_dtype, self.shift, cache.state[:, :own], ctx)
+        else:
+            h = self.mixer_norm.forward(x, ctx.act_dtype)
+        inner = cache
+        if cache.state is not None and own:
+            inner = LayerCache(kv=cache.kv, page_table=cache.page_table, page_size=cache.page_size, writes=cache.writes,
+                               state=cache.state[:, own:] if cache.state.shape[1] > own else None)
+        y = self.mixer.forward(h, ctx, inner)
+        f = bias = None
+        if self.ffn is not None:
+            xn = self.ffn_norm.add_forward(x, y, ctx.act_dtype, scale=self.mult)          # x += r * y on the way
+            bias = getattr(self.ffn, "down_bias", None)
+            f = self.ffn.forward(xn, ctx, leave_bias=True) if bias is not None else self.ffn.forward(xn, ctx)
+        else:
+            f = y
+        if hist is None:
+            K.residual_add(x, f if self.mult == 1.0 and bias is None else _scaled(f, self.mult, bias))
+            return x, None
+        K.depth_mix(hist, self.index + 1, x, self.depth, x, add=f, add_scale=self.mult, bias=bias)
+        return x, None
+
+
+def _scaled(f: torch.Tensor, mult: float, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    f = f.float() if f.dtype != torch.float32 else f
+    return K.scale_bias_cols(f, mult, None if bias is None else (bias.float() * mult).contiguous())

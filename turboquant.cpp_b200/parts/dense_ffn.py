@@ -91,22 +91,29 @@ register_feed_forward("glu", GluFeedForward)
 
 
 class ReluSquaredFeedForward(FeedForward):
-    """down(relu(up x)^2): one product up, the square of relu, one product down."""
+    """down(relu(up x)^2): one product up, the square of relu, one product down.  bias: both products have one
+    (`<name>.b`); a block that adds this part's output to the stream may take the second bias into that sum
+    (`forward(..., leave_bias=True)` and `down_bias`)."""
 
-    def __init__(self, prefix: str, hidden: int, intermediate: int, up_name: str = "up", down_name: str = "down"):
+    def __init__(self, prefix: str, hidden: int, intermediate: int, up_name: str = "up", down_name: str = "down", bias: bool = False):
         if hidden < 1 or intermediate < 1:
             raise ValueError(f"feed-forward '{prefix}': sizes must be positive, got {hidden}, {intermediate}")
         self.prefix, self.hidden, self.intermediate = prefix, int(hidden), int(intermediate)
-        self.up_name, self.down_name = up_name, down_name
-        self.w_up = self.w_down = None
+        self.up_name, self.down_name, self.has_bias = up_name, down_name, bool(bias)
+        self.w_up = self.w_down = self.up_bias = self.down_bias = None
 
     def weight_specs(self) -> List[WeightSpec]:
         p = self.prefix
-        return [WeightSpec(p + self.up_name, (self.intermediate, self.hidden)),
-                WeightSpec(p + self.down_name, (self.hidden, self.intermediate))]
+        specs = [WeightSpec(p + self.up_name, (self.intermediate, self.hidden)),
+                 WeightSpec(p + self.down_name, (self.hidden, self.intermediate))]
+        if self.has_bias:
+            specs += [WeightSpec(p + self.up_name + ".b", (self.intermediate,)), WeightSpec(p + self.down_name + ".b", (self.hidden,))]
+        return specs
 
     def bind(self, store: WeightStore) -> None:
         self.w_up, self.w_down = store.get(self.prefix + self.up_name), store.get(self.prefix + self.down_name)
+        if self.has_bias:
+            self.up_bias, self.down_bias = store.get(self.prefix + self.up_name + ".b"), store.get(self.prefix + self.down_name + ".b")
 
     def kernels(self) -> List[str]:
         return ["elementwise"]
@@ -115,11 +122,17 @@ class ReluSquaredFeedForward(FeedForward):
         wb = lambda w: 0 if w is None else w.numel() * w.element_size()
         return {"matmul": (wb(self.w_up) + wb(self.w_down), 4.0 * n_tokens * self.hidden * self.intermediate)}
 
-    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, xn: torch.Tensor, ctx: StepContext, leave_bias: bool = False) -> torch.Tensor:
         u = linear(xn, self.w_up, out_dtype=torch.float32)          # fp32 until the activation has been taken
         h = torch.empty((xn.shape[0], self.intermediate), dtype=ctx.act_dtype, device=xn.device)
-        K.map_elements(u, h, K.MAP_RELU_SQUARED)
-        return linear(h, self.w_down, out_dtype=torch.float32)
+        if self.up_bias is not None:
+            K.bias_map(u, self.up_bias, h, K.MAP_RELU_SQUARED)
+        else:
+            K.map_elements(u, h, K.MAP_RELU_SQUARED)
+        y = linear(h, self.w_down, out_dtype=torch.float32)
+        if self.down_bias is not None and not leave_bias:
+            K.add_bias(y, self.down_bias)
+        return y
 
 
 register_feed_forward("relu2", ReluSquaredFeedForward)

@@ -68,3 +68,53 @@ class RMSNorm(Norm):
         return True, None
 
 register_norm("rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Norm):
+    """A norm without statistics: y = tanh(alpha * x) * w + b, with a learned scalar alpha (tensor `<name>.alpha`), a
+    weight `<name>` and a bias `<name>.b`.  Reads the fp32 residual stream; computed in fp32.  The sums that other
+    norms take along (`add`, `add_forward`) may carry a factor: x += scale * y.  `shifted()` mixes every token's
+    output with that of the token before it (see there)."""
+
+    def __init__(self, name: str, size: int):
+        if size < 1:
+            raise ValueError(f"DynamicTanh '{name}': size {size} must be positive")
+        self.name, self.size = name, int(size)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.alpha = 1.0
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.name, (self.size,), init="one_plus_normal"), WeightSpec(self.name + ".b", (self.size,)),
+                WeightSpec(self.name + ".alpha", (), init="one_plus_normal")]
+
+    def bind(self, store: WeightStore) -> None:
+        self.weight, self.bias = store.get(self.name), store.get(self.name + ".b")
+        if self.bias.dtype != self.weight.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+        self.alpha = float(store.get(self.name + ".alpha").float().item())
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"]
+
+    def forward(self, x, out_dtype, rows=None, add=None, add_scale: float = 1.0):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.size), dtype=out_dtype, device=x.device)
+        return K.dyt(x, self.alpha, self.weight, self.bias, out, add=add, add_scale=add_scale, rows=rows)
+
+    def add_forward(self, x, y, out_dtype, scale: float = 1.0):
+        out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
+        return K.dyt(x, self.alpha, self.weight, self.bias, out, add=y, add_scale=scale)
+
+    def shifted(self, x, out_dtype, shift: torch.Tensor, kept: torch.Tensor, ctx) -> torch.Tensor:
+        """h_t + (h_(t-1) - h_t) * shift with h = this norm of x: h_(t-1) is the row above inside a sequence's run of
+        new tokens and the sequence's kept row (kept [max_slots, size] float32, zero at its start) for the run's
+        first token; the kept rows then take the runs' last outputs."""
+        out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
+        if shift.dtype != self.weight.dtype:
+            shift = shift.to(self.weight.dtype)
+        return K.dyt(x, self.alpha, self.weight, self.bias, out, shift=shift, state=kept, seq_of_token=ctx.seq_of_token,
+                     cu_seqlens=ctx.cu_seqlens, slots=ctx.slots, single_tokens=ctx.max_q_len == 1)
+
+
+register_norm("dyt", DynamicTanh)

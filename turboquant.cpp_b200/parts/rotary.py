@@ -55,9 +55,14 @@ class ScaledRotaryEncoding(PositionEncoding):
     in float32 from the frequencies (`freq`, float32 [dims/2] on the device) and the factor `mag`."""
 
     def __init__(self, dims: int, base: float, factor: Optional[float] = None, original: float = 0.0,
-                 fast: float = 0.0, slow: float = 0.0):
+                 fast: float = 0.0, slow: float = 0.0, pairing: str = "neighbours"):
+        """pairing: 'neighbours' rotates (2i, 2i+1), 'halves' (i, i + dims/2); kernels that rotate from `freq`
+        ask `halves`, `apply()` knows neighbours only."""
         if dims % 2 or dims < 0:
             raise ValueError(f"rotary: {dims} rotated dimensions must be even")
+        if pairing not in ("neighbours", "halves"):
+            raise ValueError(f"rotary: pairing must be 'neighbours' or 'halves', got '{pairing}'")
+        self.pairing = pairing
         if not base > 0:
             raise ValueError(f"rotary: base {base} must be positive")
         self.dims, self.base = int(dims), float(base)
@@ -83,10 +88,16 @@ class ScaledRotaryEncoding(PositionEncoding):
     def kernels(self):
         return ["elementwise"]
 
+    @property
+    def halves(self) -> bool:
+        return self.pairing == "halves"
+
     def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], positions: torch.Tensor) -> None:
         from ..kernels import elementwise as K
         if self.dims == 0:
             return
+        if self.halves:
+            raise NotImplementedError("rotary: pairs of halves are rotated by the kernels that read `freq`")
         K.rotate_pairs(q, self.freq, positions, self.mag)
         if k is not None:
             K.rotate_pairs(k, self.freq, positions, self.mag)
