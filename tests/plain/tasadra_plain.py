@@ -181,6 +181,20 @@ def short_convolution(u, taps_w):
     return out
 
 
+def delta_rule(q, k, v, beta, decay, S=None):
+    """One head: q, k [T, dim] (already unit vectors), v [T, vdim], beta [T], decay [T, dim]; S [dim, vdim] the state
+    before the first token (zeros if None).  Returns (outputs [T, vdim], the state after the last token)."""
+    T, dim = k.shape
+    S = np.zeros((dim, v.shape[1]), dtype=F) if S is None else S.astype(F).copy()
+    out = np.zeros((T, v.shape[1]), dtype=F)
+    for t in range(T):
+        S = decay[t][:, None] * S                     # every key channel's row decays by its own factor
+        u = beta[t] * (v[t] - S.T @ k[t])             # what the state lacks of the value, as far as beta allows
+        S = S + np.outer(k[t], u)
+        out[t] = S.T @ q[t]                           # the read-out sees the token's own write
+    return out, S
+
+
 def delta_mixer(h, w, p, m, eps):
     T = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -196,12 +210,7 @@ def delta_mixer(h, w, p, m, eps):
     out = np.zeros((T, H, vdim), dtype=F)
     for a in range(H):
         g = a // (H // G)
-        S = np.zeros((dim, vdim), dtype=F)
-        for t in range(T):
-            S = decay[t, a][:, None] * S
-            u = beta[t, a] * (v[t, a] - S.T @ k[t, g])
-            S = S + np.outer(k[t, g], u)
-            out[t, a] = S.T @ q[t, g]
+        out[:, a], _ = delta_rule(q[:, g], k[:, g], v[:, a], beta[:, a], decay[:, a])
     out = unit_rms(out, eps) * w[p + "norm"] * gate
     return out.reshape(T, H * vdim) @ w[p + "o"].T
 
@@ -213,6 +222,20 @@ def differential_keys_values(h, w, p, m):
     return (h @ w[p + "k"].T).reshape(T, G, 2, dim), (h @ w[p + "v"].T).reshape(T, G, vdim)
 
 
+def differential_combine(a1, a2, lam, eps, diff):
+    """Two maps' outputs of one head [T, vdim]: their difference, divided by its root mean square, times 1 - diff."""
+    return unit_rms(a1 - lam * a2, eps) * (1.0 - diff)
+
+
+def cell_mask(positions_q, positions_k, size):
+    """seen[i, j]: key j is not ahead of query i and, with cells of `size` positions counted from position 0, lies in
+    the query's own cell."""
+    seen = positions_k[None, :] <= positions_q[:, None]
+    if size:
+        seen = seen & (positions_k[None, :] // size == positions_q[:, None] // size)
+    return seen
+
+
 def differential_mixer(h, w, p, m, eps, kv=None):
     """kv: (keys, values) of the layer this one reads, or None if it has projections of its own."""
     T = h.shape[0]
@@ -220,18 +243,14 @@ def differential_mixer(h, w, p, m, eps, kv=None):
     pos = np.arange(T)
     q = (h @ w[p + "q"].T).reshape(T, H, 2, dim)
     k, v = kv if kv is not None else differential_keys_values(h, w, p, m)
-    size = m["mask"]["size"] if m.get("mask") else None
-    seen = pos[None, :] <= pos[:, None]
-    if size:
-        seen = seen & (pos[None, :] // size == pos[:, None] // size)
+    seen = cell_mask(pos, pos, m["mask"]["size"] if m.get("mask") else 0)
     diff = float(m["diff"])
     lam = math.exp(float(np.sum(w[p + "lq1"] * w[p + "lk1"]))) - math.exp(float(np.sum(w[p + "lq2"] * w[p + "lk2"]))) + diff
     out = np.zeros((T, H, vdim), dtype=F)
     for a in range(H):
         g = a // (H // G)
         maps = [softmax_rows((q[:, a, i] @ k[:, g, i].T) * m["scale"], seen) @ v[:, g] for i in range(2)]
-        out[:, a] = maps[0] - lam * maps[1]
-    out = unit_rms(out, eps) * (1.0 - diff)
+        out[:, a] = differential_combine(maps[0], maps[1], lam, eps, diff)
     out = out.reshape(T, H * vdim) * sigmoid(h @ w[p + "g"].T)
     return out @ w[p + "o"].T
 
@@ -273,3 +292,13 @@ def forward(cfg, w, tokens, streams=None):
         if streams is not None:
             streams.append(x)
     return dyt(x, w, "final.norm") @ w["head"].T
+
+
+class PlainTasadra:
+    """A model folder and its logits."""
+
+    def __init__(self, folder):
+        self.cfg, self.w = load(folder)
+
+    def forward(self, tokens, streams=None):
+        return forward(self.cfg, self.w, tokens, streams)
