@@ -150,7 +150,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
                     "prefill to this file (torch profiler; not part of any timed number)")
-    ap.add_argument("--design", choices=["nuforax", "lumevik", "sisepel"], default="", help="instead of the default workload: prompt "
+    ap.add_argument("--design", choices=["nuforax", "lumevik", "sisepel", "tasadra"], default="", help="instead of the default workload: prompt "
                     "and decode speed of this design at layer sizes of a real model (random weights), beside the closest other "
                     "decoder of equal width, depth and heads")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of the sizes to run")
@@ -481,6 +481,8 @@ def design_compare(args) -> int:
         return lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
     if args.design == "sisepel":
         return sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
+    if args.design == "tasadra":
+        return tasadra_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
     result = {"metric": "prompt and decode speed, Nuforax beside the dense Qwen2 decoder of equal width", "unit": "tokens/s",
               "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
               "peaks": pk, "sizes": {}}
@@ -577,6 +579,74 @@ def sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, wa
                     "experts": E, "top": top, "expert_ff": e_ff, "shared_ff": s_ff}
             if who == "sisepel":
                 conf.update(retention={"heads": rh, "dim": rd, "vdim": rv}, token_input=side)
+            entry[who] = dict(measure(model, V), config=conf)
+            if args.kernel_table:
+                kernel_table(tq, model, rng, V, args.batch, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        result["sizes"][name] = entry
+    result["clocks"] = clocks.stop()
+    print(json.dumps(result))
+    return 0
+
+
+def tasadra_config(width, heads, kv_heads, dim, d_dim, cell, ff, vocab, ranks=(64, 64)):
+    """Six layers: attention, delta rule, differential attention in cells, attention, differential attention reading
+    the first one's rows, delta rule; a dense feed-forward on every layer."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+           "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    rule = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": ranks[0], "gate_rank": ranks[1]}
+    dif = lambda src: dict({"heads": heads, "kv_heads": kv_heads, "dim": d_dim, "vdim": dim, "scale": d_dim ** -0.5, "diff": 0.3,
+                            "mask": {"size": cell}}, **({} if src is None else {"kv_from": src}))
+    mlp = {"kind": "dense", "ff": ff}
+    kinds = [("attention", att), ("channel_delta", rule), ("attention_2", dif(None)), ("attention", att),
+             ("attention_2", dif(2)), ("channel_delta", rule)]
+    return {"architecture": "Tasadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "layers": [{"type": k, "mixer": m, "mlp": mlp} for k, m in kinds]}
+
+
+def sisepel_dense_config(width, layers, heads, kv_heads, dim, window, r_heads, r_dim, r_vdim, ff, vocab):
+    """The Sisepel decoder with a dense feed-forward on every layer and no token input."""
+    cfg = sisepel_config(width, layers, heads, kv_heads, dim, window, r_heads, r_dim, r_vdim, ff, 1, 1, 1, 1, 1, vocab)
+    cfg.pop("token_side")
+    for l in cfg["layers"]:
+        l["mlp"] = {"kind": "dense", "ff": ff}
+    return cfg
+
+
+TASADRA_SIZES = {
+    # name: (width, heads, kv heads, head size, key size of the differential layers, cells, feed-forward, vocab,
+    #        the sibling's retention heads, key size, value size)
+    "w1024": (1024, 8, 2, 128, 64, 1024, 4096, 32768, 8, 64, 128),
+    "w2048": (2048, 16, 4, 128, 64, 1024, 8192, 32768, 16, 128, 128),
+}
+
+
+def tasadra_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup) -> int:
+    """The Tasadra decoder beside the Sisepel decoder of the same width, depth, heads, head size and dense feed-forward:
+    both run softmax attention over rows of keys and values on the same kernels and a recurrence with a state per
+    head; Sisepel has both on every layer, Tasadra one of them a layer."""
+    import torch
+    result = {"metric": "prompt and decode speed, Tasadra beside the Sisepel decoder of equal sizes", "unit": "tokens/s",
+              "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+              "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.sizes.split(","):
+        if name not in TASADRA_SIZES:
+            print(json.dumps({"error": f"unknown size '{name}'; known: {sorted(TASADRA_SIZES)}"}))
+            return 2
+        (W, H, G, D, DD, cell, ff, V, rh, rd, rv) = TASADRA_SIZES[name]
+        entry = {}
+        for who, cfg in (("tasadra", tasadra_config(W, H, G, D, DD, cell, ff, V)),
+                         ("sisepel", sisepel_dense_config(W, 6, H, G, D, cell, rh, rd, rv, ff, V))):
+            model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            conf = {"width": W, "layers": 6, "heads": H, "kv_heads": G, "head_size": D, "dense_ff": ff}
+            if who == "tasadra":
+                conf.update(differential={"dim": DD, "cells": cell}, delta={"heads": H, "dim": D, "vdim": D, "conv": 4})
+            else:
+                conf.update(window=cell, retention={"heads": rh, "dim": rd, "vdim": rv})
             entry[who] = dict(measure(model, V), config=conf)
             if args.kernel_table:
                 kernel_table(tq, model, rng, V, args.batch, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
