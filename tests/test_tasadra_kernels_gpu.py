@@ -283,11 +283,13 @@ DELTA_CASES = [
     (3, 1, 100, 16),
     (1, 1, 200, 21),
     (2, 1, 1, 1),
+    (2, 2, 128, 128),
 ]
 
 
+@pytest.mark.parametrize("form", ["delta_scan", "delta_scan_runs"])
 @pytest.mark.parametrize("case", DELTA_CASES)
-def test_delta_rule_over_portions_in_used_slots(case):
+def test_delta_rule_over_portions_in_used_slots(case, form):
     from turboquant_cpp_b200.kernels import ssm as KS
     H, G, dk, dv = case
     rng = np.random.default_rng(dk * 10 + dv)
@@ -323,7 +325,7 @@ def test_delta_rule_over_portions_in_used_slots(case):
         parts = [np.concatenate([data[i][j][done[i]:done[i] + n] for i, n in zip(live, take)]) for j in range(3)]
         cu = np.concatenate([[0], np.cumsum(take)])
         y = torch.full((int(cu[-1]), H * dv), float("nan"), device=DEV)
-        KS.delta_scan(dev(parts[0]), 0, G * dk, 2 * G * dk, dev(parts[1]), b_off, dev(parts[2]), a_off, dev(dt_bias), dev(a_log),
+        getattr(KS, form)(dev(parts[0]), 0, G * dk, 2 * G * dk, dev(parts[1]), b_off, dev(parts[2]), a_off, dev(dt_bias), dev(a_log),
                       state, y, H, G, dk, dv, unit_eps, q_scale, i32(cu), i32([slots[i] for i in live]))
         ref = np.concatenate([want[i][0][done[i]:done[i] + n] for i, n in zip(live, take)])
         assert rel(y, ref) < 3e-5, portion

@@ -917,8 +917,11 @@ TQ_EXPORT int tq_dyt(float* x, const void* y, int y_dtype, float scale, const in
                                     cu_seqlens != nullptr && slots != nullptr),
                "dyt: the shift wants whole steps, the sequences' kept rows and no sum on the way");
     if (y == nullptr) y_dtype = TQ_F32;
+    // an element a thread: two tanhf each with the shift, and steps of a few rows still fill the GPU
     const int threads = H >= 1024 ? 256 : 128;
-    dim3 grid(R, (H + 8 * threads - 1) / (8 * threads));
+    const int per_thread = R >= 256 ? 4 : 1;                  // long steps have blocks enough
+    dim3 grid(R, (H + per_thread * threads - 1) / (per_thread * threads));
+    TQ_REQUIRE(grid.y <= 65535, "dyt: rows of %d elements exceed the grid limit", H);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(grid, threads, 0, stream)(dyt_kernel<TY, TW, TO>, x, (const TY*)y, scale, rows, alpha, (const TW*)w, (const TW*)b,
             (TO*)out, H, (const TW*)shift, state, slot_stride, seq_of_token, cu_seqlens, slots, keep)))));

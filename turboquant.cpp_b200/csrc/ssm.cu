@@ -772,3 +772,214 @@ TQ_EXPORT int tq_delta_scan(const float* xqkv, int C, int q_off, int k_off, int 
     TQ_CHECK_LAUNCH("delta_scan");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// The delta rule for runs of many tokens, in two launches.
+//   delta_prepare: what the recurrence reads, for all tokens side by side: per token a row of `R` floats
+//                  [k: G x dk unit vectors | q: G x dk unit vectors times q_scale | g: H x dk decays | k.q: G | beta: H]
+//                  (R rounded up to a multiple of four).  A warp per (token, query/key head) and per (token, head).
+//   delta_scan_rows: the recurrence over those rows.  Same grid and ownership of the state as delta_scan; a chunk's
+//                  rows come through cp.async into one of two buffers in shared memory while the chunk before is
+//                  computed.  Per token both read-outs are taken from the decayed state BEFORE the write,
+//                  pred = (gS)^T k and r = (gS)^T q, their two chains of shuffles side by side, and the output is
+//                  o = r + (k.q) u: the same sum as (gS + k u^T)^T q, with one round of shuffles on the path from a
+//                  token's state to the next token's instead of two.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const float* __restrict__ xqkv, int C, int q_off, int k_off, const float* __restrict__ proj, int P, int b_off,
+                     const float* __restrict__ a_raw, int A, int a_off, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, float* __restrict__ rows, int R, int T_, int heads, int kv_heads, int dk,
+                     float unit_eps, float q_scale) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31, item = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const size_t t = blockIdx.x;
+    if (item >= kv_heads + heads) return;
+    float* out = rows + t * R;
+    const int g_at = 2 * kv_heads * dk, kq_at = g_at + heads * dk, b_at = kq_at + kv_heads;
+    if (item < kv_heads) {
+        const float* kr = xqkv + t * C + k_off + (size_t)item * dk;
+        const float* qr = xqkv + t * C + q_off + (size_t)item * dk;
+        float ssk = 0.f, ssq = 0.f;
+        for (int e = lane; e < dk; e += 32) { const float a = kr[e], b = qr[e]; ssk += a * a; ssq += b * b; }
+        ssk = tq_warp_sum(ssk); ssq = tq_warp_sum(ssq);
+        const float rk = 1.0f / sqrtf(ssk + unit_eps), rq = q_scale / sqrtf(ssq + unit_eps);
+        for (int e = lane; e < dk; e += 32) {
+            out[(size_t)item * dk + e] = kr[e] * rk;
+            out[(size_t)(kv_heads + item) * dk + e] = qr[e] * rq;
+        }
+        // k.q of the vectors as they are written: summed again from the rounded values the recurrence will read
+        float kq = 0.f;
+        for (int e = lane; e < dk; e += 32) kq += (kr[e] * rk) * (qr[e] * rq);
+        kq = tq_warp_sum(kq);
+        if (lane == 0) out[kq_at + item] = kq;
+    } else {
+        const int h = item - kv_heads;
+        const float rate = expf(a_log[h]);
+        const float* ar = a_raw + t * A + a_off + (size_t)h * dk;
+        for (int e = lane; e < dk; e += 32) {
+            const float z = ar[e] + dt_bias[(size_t)h * dk + e];
+            const float sp = z > 20.f ? z : log1pf(expf(z));
+            out[g_at + (size_t)h * dk + e] = expf(-rate * sp);
+        }
+        if (lane == 0) out[b_at + h] = 1.0f / (1.0f + expf(-proj[t * P + b_off + h]));
+    }
+}
+
+__device__ __forceinline__ void delta_copy4(float* smem_dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void delta_copy16(float* smem_dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+
+template <int RPL>
+__global__ void __launch_bounds__(128)
+delta_scan_rows_kernel(const float* __restrict__ rows, int R, const float* __restrict__ xqkv, int C, int v_off,
+                       float* __restrict__ state, long long slot_stride, float* __restrict__ y, int heads, int kv_heads,
+                       int dk, int dv, int tc, int vec, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int DKP = RPL * 8;
+    extern __shared__ __align__(16) float delta_rows_smem[];
+    const int per_buf = tc * (3 * DKP + DELTA_COLS + 4);       // k, q, g rows, values, k.q, beta (and two unused) per token
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
+    const int lc = warp * 4 + (lane >> 3), col = c0 + lc;
+    const bool live = col < dv;
+    const int g = h / (heads / kv_heads);
+    const int t0 = cu_seqlens[s], n = cu_seqlens[s + 1] - t0;
+    const int g_at = 2 * kv_heads * dk, kq_at = g_at + heads * dk, b_at = kq_at + kv_heads;
+    for (int i = threadIdx.x; i < 2 * per_buf; i += blockDim.x) delta_rows_smem[i] = 0.f;      // rows beyond dk stay zero
+    __syncthreads();
+    float* Sp = state + (size_t)slots[s] * slot_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
+    float S[RPL];
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+        const int row = sub + 8 * r;
+        S[r] = live && row < dk ? Sp[row] : 0.f;
+    }
+    auto fetch = [&](int base, int buf) {
+        float* b = delta_rows_smem + (size_t)buf * per_buf;
+        float* bk = b; float* bq = bk + tc * DKP; float* bg = bq + tc * DKP; float* bv = bg + tc * DKP; float* bs = bv + tc * DELTA_COLS;
+        const int nt = min(tc, n - base);
+        if (vec) {
+            const int q4 = dk >> 2;
+            for (int i = threadIdx.x; i < nt * q4; i += blockDim.x) {
+                const int tk = i / q4, e = (i - tk * q4) * 4;
+                const float* src = rows + ((size_t)t0 + base + tk) * R;
+                delta_copy16(bk + tk * DKP + e, src + (size_t)g * dk + e);
+                delta_copy16(bq + tk * DKP + e, src + (size_t)(kv_heads + g) * dk + e);
+                delta_copy16(bg + tk * DKP + e, src + g_at + (size_t)h * dk + e);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * dk; i += blockDim.x) {
+                const int tk = i / dk, e = i - tk * dk;
+                const float* src = rows + ((size_t)t0 + base + tk) * R;
+                delta_copy4(bk + tk * DKP + e, src + (size_t)g * dk + e);
+                delta_copy4(bq + tk * DKP + e, src + (size_t)(kv_heads + g) * dk + e);
+                delta_copy4(bg + tk * DKP + e, src + g_at + (size_t)h * dk + e);
+            }
+        }
+        for (int i = threadIdx.x; i < nt * (DELTA_COLS + 2); i += blockDim.x) {
+            const int tk = i / (DELTA_COLS + 2), e = i - tk * (DELTA_COLS + 2);
+            const size_t t = (size_t)t0 + base + tk;
+            if (e < DELTA_COLS) {
+                if (c0 + e < dv) delta_copy4(bv + tk * DELTA_COLS + e, xqkv + t * C + v_off + (size_t)h * dv + c0 + e);
+            } else if (e == DELTA_COLS) {
+                delta_copy4(bs + tk * 4, rows + t * R + kq_at + g);
+            } else {
+                delta_copy4(bs + tk * 4 + 1, rows + t * R + b_at + h);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n > 0) fetch(0, 0);
+    int buf = 0;
+    for (int base = 0; base < n; base += tc, buf ^= 1) {
+        const int nt = min(tc, n - base);
+        if (base + tc < n) {
+            fetch(base + tc, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* b = delta_rows_smem + (size_t)buf * per_buf;
+        const float* bk = b + sub; const float* bq = bk + tc * DKP; const float* bg = bq + tc * DKP;
+        const float* bv = b + 3 * tc * DKP; const float* bs = bv + tc * DELTA_COLS;
+        for (int i = 0; i < nt; ++i) {
+            float kreg[RPL];
+            float p0 = 0.f, p1 = 0.f, r0 = 0.f, r1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < RPL; r += 2) {
+                kreg[r] = bk[i * DKP + 8 * r];
+                kreg[r + 1] = bk[i * DKP + 8 * (r + 1)];
+                S[r] *= bg[i * DKP + 8 * r];
+                S[r + 1] *= bg[i * DKP + 8 * (r + 1)];
+                p0 += S[r] * kreg[r];
+                p1 += S[r + 1] * kreg[r + 1];
+                r0 += S[r] * bq[i * DKP + 8 * r];
+                r1 += S[r + 1] * bq[i * DKP + 8 * (r + 1)];
+            }
+            float pred = p0 + p1, rd = r0 + r1;
+            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+            rd += __shfl_xor_sync(0xffffffffu, rd, 1);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+            rd += __shfl_xor_sync(0xffffffffu, rd, 2);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 4);
+            rd += __shfl_xor_sync(0xffffffffu, rd, 4);
+            const float u = bs[i * 4 + 1] * (bv[i * DELTA_COLS + lc] - pred);
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) S[r] += kreg[r] * u;
+            if (sub == 0 && live) y[((size_t)t0 + base + i) * heads * dv + (size_t)h * dv + col] = rd + bs[i * 4] * u;
+        }
+        __syncthreads();                 // the buffer is free for the chunk after the next
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RPL; ++r) {
+            const int row = sub + 8 * r;
+            if (row < dk) Sp[row] = S[r];
+        }
+    }
+}
+
+TQ_EXPORT int tq_delta_rows_width(int heads, int kv_heads, int dk) {
+    return (2 * kv_heads * dk + heads * dk + kv_heads + heads + 3) / 4 * 4;
+}
+
+// The two launches; `rows` is scratch of T * tq_delta_rows_width() floats.  Arguments as for tq_delta_scan.
+TQ_EXPORT int tq_delta_scan_runs(const float* xqkv, int C, int q_off, int k_off, int v_off, const float* proj, int P, int b_off,
+                                 const float* a_raw, int A, int a_off, const float* dt_bias, const float* a_log, float* rows,
+                                 float* state, long long slot_stride, float* y, int T_, int n_seqs, int heads, int kv_heads,
+                                 int dk, int dv, float unit_eps, float q_scale, const int* cu_seqlens, const int* slots,
+                                 cudaStream_t stream) {
+    if (n_seqs == 0 || T_ == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && kv_heads >= 1 && heads % kv_heads == 0 && heads <= 65535, "delta_scan_runs: %d heads on %d query/key heads", heads, kv_heads);
+    TQ_REQUIRE(dk >= 1 && dk <= SSM_MAX_STATE && dv >= 1, "delta_scan_runs: keys of %d elements (1..%d), values of %d", dk, SSM_MAX_STATE, dv);
+    TQ_REQUIRE(q_off >= 0 && k_off >= 0 && v_off >= 0 && q_off + kv_heads * dk <= C && k_off + kv_heads * dk <= C && v_off + heads * dv <= C,
+               "delta_scan_runs: queries, keys or values lie outside rows of %d", C);
+    TQ_REQUIRE(b_off >= 0 && b_off + heads <= P && a_off >= 0 && a_off + heads * dk <= A, "delta_scan_runs: betas or decays lie outside their rows");
+    TQ_REQUIRE(rows != nullptr, "delta_scan_runs: no scratch for the prepared rows");
+    const int R = tq_delta_rows_width(heads, kv_heads, dk);
+    tq_launch(dim3(T_, (kv_heads + heads + 3) / 4), 128, 0, stream)(delta_prepare_kernel, xqkv, C, q_off, k_off, proj, P, b_off, a_raw, A,
+        a_off, dt_bias, a_log, rows, R, T_, heads, kv_heads, dk, unit_eps, q_scale);
+    TQ_CHECK_LAUNCH("delta_prepare");
+    const int rpl = dk <= 64 ? 8 : (dk <= 128 ? 16 : 32);
+    const int tc = rpl <= 16 ? 16 : 8;
+    const size_t smem = (size_t)2 * tc * (3 * rpl * 8 + DELTA_COLS + 4) * sizeof(float);
+    const int vec = dk % 4 == 0 && ((uintptr_t)rows & 15) == 0;
+    dim3 grid(n_seqs, heads, (dv + DELTA_COLS - 1) / DELTA_COLS);
+    TQ_REQUIRE(grid.z <= 65535, "delta_scan_runs: values of %d elements exceed the grid limit", dv);
+#define DELTA_ROWS_LAUNCH(RP)                                                                                          \
+    do {                                                                                                               \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_rows_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        tq_launch(grid, 128, smem, stream)(delta_scan_rows_kernel<RP>, (const float*)rows, R, xqkv, C, v_off, state, slot_stride, y, \
+            heads, kv_heads, dk, dv, tc, vec, cu_seqlens, slots);                                                      \
+    } while (0)
+    if (rpl == 8) DELTA_ROWS_LAUNCH(8); else if (rpl == 16) DELTA_ROWS_LAUNCH(16); else DELTA_ROWS_LAUNCH(32);
+#undef DELTA_ROWS_LAUNCH
+    TQ_CHECK_LAUNCH("delta_scan_rows");
+    return 0;
+}

@@ -193,3 +193,31 @@ def delta_scan(xqkv: torch.Tensor, q_off: int, k_off: int, v_off: int, proj: tor
                                   c_int(cu_seqlens.shape[0] - 1), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
                                   c_float(unit_eps), c_float(q_scale), ptr(cu_seqlens), ptr(slots), stream()))
     return y
+
+
+def delta_scan_runs(xqkv: torch.Tensor, q_off: int, k_off: int, v_off: int, proj: torch.Tensor, b_off: int, a_raw: torch.Tensor,
+                    a_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, y: torch.Tensor, heads: int,
+                    kv_heads: int, dk: int, dv: int, unit_eps: float, q_scale: float, cu_seqlens: torch.Tensor,
+                    slots: torch.Tensor) -> torch.Tensor:
+    """`delta_scan` for steps with runs of many tokens, in two launches: the unit vectors, decays and betas of all
+    tokens side by side into rows of scratch, then the recurrence over those rows (a chunk of rows copied into shared
+    memory while the chunk before is computed).  Arguments and result as for `delta_scan`; the sums are the same
+    up to their order."""
+    for t, what in ((xqkv, "q, k and v"), (proj, "the projection"), (a_raw, "the raw decays"), (dt_bias, "the decays' bias"),
+                    (a_log, "the decay rates"), (state, "the state"), (y, "the output")):
+        want_f32(t, what)
+    want_int32(cu_seqlens, "the sequences' bounds")
+    want_int32(slots, "slots")
+    if tuple(state.shape[1:]) != (heads, dv, dk) or not state[0].is_contiguous():
+        raise KernelError("delta_scan_runs: the state must be [slots, heads, vdim, dim] with dense rows")
+    if dt_bias.numel() != heads * dk or a_log.numel() != heads or y.shape != (xqkv.shape[0], heads * dv):
+        raise KernelError("delta_scan_runs: one decay bias per head and key channel, one rate per head, an output of heads*dv")
+    lib = load_kernel(_LIB)
+    T = xqkv.shape[0]
+    rows = torch.empty((T, int(lib.tq_delta_rows_width(c_int(heads), c_int(kv_heads), c_int(dk)))), dtype=torch.float32, device=xqkv.device)
+    check(_LIB, lib.tq_delta_scan_runs(ptr(xqkv), c_int(xqkv.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), ptr(proj),
+                                       c_int(proj.shape[1]), c_int(b_off), ptr(a_raw), c_int(a_raw.shape[1]), c_int(a_off),
+                                       ptr(dt_bias), ptr(a_log), ptr(rows), ctypes_ptr(state), c_longlong(state.stride(0)), ptr(y),
+                                       c_int(T), c_int(cu_seqlens.shape[0] - 1), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+                                       c_float(unit_eps), c_float(q_scale), ptr(cu_seqlens), ptr(slots), stream()), kernels=2)
+    return y

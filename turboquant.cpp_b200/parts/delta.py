@@ -32,6 +32,8 @@ UNIT_EPS = 1e-6          # inside the root of the unit vectors of q and k
 
 
 class ChannelDeltaMixer(Mixer):
+    RUNS_MIN = 16             # steps whose longest run of new tokens is at least this take the two-launch form
+
     def __init__(self, prefix: str, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, eps: float,
                  decay_rank: int = -1, gate_rank: int = -1):
         """decay_rank, gate_rank: the inner sizes of the two low-rank pairs; -1: read from the stored tensors (a model
@@ -104,8 +106,10 @@ class ChannelDeltaMixer(Mixer):
         KS.conv_silu(proj, 0, self.w_conv, None, kept, qkv, ctx.seq_of_token, ctx.cu_seqlens, ctx.slots)
         raw = linear(proj[:, self.a1_off:self.a1_off + self.rank_a], self.w_a2, out_dtype=torch.float32)      # raw decays
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
-        KS.delta_scan(qkv, 0, self.qk_size, 2 * self.qk_size, proj, self.b_off, raw, 0, self.dt_bias, self.a_log, S, y,
-                      self.heads, self.kv_heads, self.dim, self.vdim, UNIT_EPS, self.dim ** -0.5, ctx.cu_seqlens, ctx.slots)
+        # runs of many tokens: the recurrence's inputs prepared side by side first; single tokens: one launch
+        scan = KS.delta_scan_runs if ctx.max_q_len >= self.RUNS_MIN else KS.delta_scan
+        scan(qkv, 0, self.qk_size, 2 * self.qk_size, proj, self.b_off, raw, 0, self.dt_bias, self.a_log, S, y,
+             self.heads, self.kv_heads, self.dim, self.vdim, UNIT_EPS, self.dim ** -0.5, ctx.cu_seqlens, ctx.slots)
         gate = linear(proj[:, self.g1_off:self.g1_off + self.rank_g], self.w_g2, out_dtype=torch.float32)
         o = torch.empty((T, self.inner), dtype=ctx.act_dtype, device=dev)
         KS.gated_group_norm(y, gate, 0, self.w_norm, self.heads, self.eps, o, gate_after=True, sigmoid_gate=True)
