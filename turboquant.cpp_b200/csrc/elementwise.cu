@@ -891,6 +891,54 @@ __global__ void dyt_kernel(float* __restrict__ x, const TY* __restrict__ y, floa
     }
 }
 
+// The same with four neighbouring elements a thread (rows of a multiple of four elements, 16-byte aligned): every
+// load of a thread's piece is in flight before the first tanhf.
+template <typename TY, typename TW, typename TO>
+__global__ void dyt_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, float scale, const int* __restrict__ rows, float alpha,
+                               const TW* __restrict__ w, const TW* __restrict__ b, TO* __restrict__ out, int H,
+                               const TW* __restrict__ shift, float* __restrict__ state, long long slot_stride,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
+                               const int* __restrict__ slots, int keep) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* xr = x + src * H;
+    const float* above = nullptr;
+    float* kept = nullptr;
+    if (shift != nullptr) {
+        const int s = seq_of_token[src];
+        kept = state + (size_t)slots[s] * slot_stride;
+        if ((int)src > cu_seqlens[s]) above = xr - H;
+    }
+    auto norm4 = [alpha](float4 v, float4 wi, float4 bi) {
+        return make_float4(tanhf(alpha * v.x) * wi.x + bi.x, tanhf(alpha * v.y) * wi.y + bi.y,
+                           tanhf(alpha * v.z) * wi.z + bi.z, tanhf(alpha * v.w) * wi.w + bi.w);
+    };
+    for (int i = 4 * (blockIdx.y * blockDim.x + threadIdx.x); i < H; i += 4 * gridDim.y * blockDim.x) {
+        float4 v = tq_load4<float>(xr + i);
+        const float4 wi = tq_load4<TW>(w + i), bi = tq_load4<TW>(b + i);
+        float4 before = make_float4(0.f, 0.f, 0.f, 0.f), sh = before;
+        if (shift != nullptr) {
+            before = tq_load4<float>((above ? above : kept) + i);
+            sh = tq_load4<TW>(shift + i);
+        }
+        if (y != nullptr) {
+            const float4 a = tq_load4<TY>(y + src * H + i);
+            v.x += scale * a.x; v.y += scale * a.y; v.z += scale * a.z; v.w += scale * a.w;
+            if (rows == nullptr) tq_store4<float>(xr + i, v);
+        }
+        float4 h = norm4(v, wi, bi);
+        if (shift != nullptr) {
+            if (above) before = norm4(before, wi, bi);
+            if (keep) tq_store4<float>(kept + i, h);
+            h.x += (before.x - h.x) * sh.x; h.y += (before.y - h.y) * sh.y;
+            h.z += (before.z - h.z) * sh.z; h.w += (before.w - h.w) * sh.w;
+        }
+        tq_store4<TO>(out + r * H + i, h);
+    }
+}
+
 // kept row of every sequence <- the unshifted norm of its last token of this step; grid (sequences, column chunks)
 template <typename TW>
 __global__ void dyt_keep_last_kernel(const float* __restrict__ x, float alpha, const TW* __restrict__ w, const TW* __restrict__ b,
@@ -922,9 +970,19 @@ TQ_EXPORT int tq_dyt(float* x, const void* y, int y_dtype, float scale, const in
     const int per_thread = R >= 256 ? 4 : 1;                  // long steps have blocks enough
     dim3 grid(R, (H + per_thread * threads - 1) / (per_thread * threads));
     TQ_REQUIRE(grid.y <= 65535, "dyt: rows of %d elements exceed the grid limit", H);
-    TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
-        (tq_launch(grid, threads, 0, stream)(dyt_kernel<TY, TW, TO>, x, (const TY*)y, scale, rows, alpha, (const TW*)w, (const TW*)b,
-            (TO*)out, H, (const TW*)shift, state, slot_stride, seq_of_token, cu_seqlens, slots, keep)))));
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = H % 4 == 0 && aligned(x) && aligned(y) && aligned(w) && aligned(b) && aligned(out) && aligned(shift) &&
+                     aligned(state) && slot_stride % 4 == 0;
+    if (vec) {
+        dim3 vgrid(R, (H / 4 + threads - 1) / threads);
+        TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+            (tq_launch(vgrid, threads, 0, stream)(dyt_vec_kernel<TY, TW, TO>, x, (const TY*)y, scale, rows, alpha, (const TW*)w, (const TW*)b,
+                (TO*)out, H, (const TW*)shift, state, slot_stride, seq_of_token, cu_seqlens, slots, keep)))));
+    } else {
+        TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+            (tq_launch(grid, threads, 0, stream)(dyt_kernel<TY, TW, TO>, x, (const TY*)y, scale, rows, alpha, (const TW*)w, (const TW*)b,
+                (TO*)out, H, (const TW*)shift, state, slot_stride, seq_of_token, cu_seqlens, slots, keep)))));
+    }
     TQ_CHECK_LAUNCH("dyt");
     if (shift != nullptr && !keep) {
         TQ_DISPATCH(w_dtype, TW,

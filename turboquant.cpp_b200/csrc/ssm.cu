@@ -974,7 +974,11 @@ TQ_EXPORT int tq_delta_scan_runs(const float* xqkv, int C, int q_off, int k_off,
     TQ_REQUIRE(grid.z <= 65535, "delta_scan_runs: values of %d elements exceed the grid limit", dv);
 #define DELTA_ROWS_LAUNCH(RP)                                                                                          \
     do {                                                                                                               \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_rows_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        static bool roomy = false;             /* asked for once: two chunks' rows can pass the 48 KB a kernel gets unasked */ \
+        if (smem > 48 * 1024 && !roomy) {                                                                              \
+            cudaFuncSetAttribute(delta_scan_rows_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);    \
+            roomy = true;                                                                                              \
+        }                                                                                                              \
         tq_launch(grid, 128, smem, stream)(delta_scan_rows_kernel<RP>, (const float*)rows, R, xqkv, C, v_off, state, slot_stride, y, \
             heads, kv_heads, dk, dv, tc, vec, cu_seqlens, slots);                                                      \
     } while (0)
