@@ -259,9 +259,25 @@ def test_command_line_and_trace_replay(folders, tmp_path):
     cfg, folder = CONFIGS["c"], folders["c"]
     toks = tokens_for(cfg, 40, 77)
     env = dict(os.environ, PYTHONPATH=ROOT)
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "quant"), folder, "-p", " ".join(map(str, toks[:9])), "-n", "5", "-T", "0"],
-                         capture_output=True, text=True, env=env, timeout=600)
+    import turboquant_cpp_b200 as tq
+    quant = [sys.executable, os.path.join(ROOT, "bin", "quant")]
+    common = ["-p", " ".join(map(str, toks[:9])), "-n", "5", "-T", "0", "--dtype", "float32"]
+    out = subprocess.run(quant + [folder] + common, capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
+    with tq.Model(folder, temperature=0.0, max_tokens=5, dtype="float32") as m:
+        assert [int(t) for t in out.stdout.split()] == m.ask(toks[:9])
+    info = subprocess.run(quant + [folder, "--info"], capture_output=True, text=True, env=env, timeout=600)
+    assert info.returncode == 0 and "Tasadra" in info.stdout
+    # weights drawn at random need the inner sizes of the delta rule's low-rank pairs, which a file gives by its tensors
+    given = copy.deepcopy(cfg)
+    for l in given["layers"]:
+        if l["type"] == "channel_delta":
+            l["mixer"].update(decay_rank=3, gate_rank=5)
+    json.dump(given, open(tmp_path / "cfg.json", "w"))
+    runs = [subprocess.run(quant + ["--random", str(tmp_path / "cfg.json"), "--seed-weights", str(seed)] + common + ["--profile"],
+                           capture_output=True, text=True, env=env, timeout=600) for seed in (3, 4)]
+    assert all(x.returncode == 0 for x in runs), runs[0].stderr[-2000:] + runs[1].stderr[-2000:]
+    assert any(l.startswith("[Profile ") and "matmul=" in l for l in runs[0].stderr.splitlines())
     steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:30], "want": [0, 29]}], "end": []},
              {"step": 1, "entries": [{"id": "x", "tokens": toks[30:32], "want": []}], "end": []},
              {"step": 2, "entries": [{"id": "x", "tokens": toks[32:], "want": [7]}], "end": ["x"]}]
