@@ -193,6 +193,8 @@ struct TqLaunch {
     size_t smem;
     cudaStream_t stream;
     unsigned cluster;          // CTAs per cluster along x (1: no clusters)
+    bool early;                // false: the kernel starts only when the kernel ahead has ended, on an empty GPU (a long kernel of few
+                               // CTAs that should lie one an SM: launched early they are packed onto the SMs that have room first)
     void config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr) const {
         static const bool pdl = [] { const char* e = getenv("TQ_NO_PDL"); return !(e && e[0] && e[0] != '0'); }();
         cfg = cudaLaunchConfig_t{};
@@ -201,7 +203,7 @@ struct TqLaunch {
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         unsigned n = 0;
-        if (pdl) {
+        if (pdl && early) {
             attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[n].val.programmaticStreamSerializationAllowed = 1;
             ++n;
@@ -224,8 +226,8 @@ struct TqLaunch {
         cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in TQ_CHECK_LAUNCH
     }
 };
-inline TqLaunch tq_launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster = 1) {
-    return TqLaunch{grid, block, smem, stream, cluster};
+inline TqLaunch tq_launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster = 1, bool early = true) {
+    return TqLaunch{grid, block, smem, stream, cluster, early};
 }
 
 // Dispatch on an element type code: TQ_F32 -> float, TQ_BF16 -> __nv_bfloat16.

@@ -972,6 +972,12 @@ TQ_EXPORT int tq_delta_scan_runs(const float* xqkv, int C, int q_off, int k_off,
     const int vec = dk % 4 == 0 && ((uintptr_t)rows & 15) == 0;
     dim3 grid(n_seqs, heads, (dv + DELTA_COLS - 1) / DELTA_COLS);
     TQ_REQUIRE(grid.z <= 65535, "delta_scan_runs: values of %d elements exceed the grid limit", dv);
+    // Up to an SM's worth of blocks start on an empty GPU, one an SM: launched while the preparation still runs they are
+    // packed four an SM where room is first, and the shared-memory pipe they then share makes the scan 2.3 times as long.
+    int n_sms = 0, device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+    const bool few_blocks = (long long)grid.x * grid.y * grid.z <= 2LL * n_sms;
 #define DELTA_ROWS_LAUNCH(RP)                                                                                          \
     do {                                                                                                               \
         static bool roomy = false;             /* asked for once: two chunks' rows can pass the 48 KB a kernel gets unasked */ \
@@ -979,7 +985,7 @@ TQ_EXPORT int tq_delta_scan_runs(const float* xqkv, int C, int q_off, int k_off,
             cudaFuncSetAttribute(delta_scan_rows_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);    \
             roomy = true;                                                                                              \
         }                                                                                                              \
-        tq_launch(grid, 128, smem, stream)(delta_scan_rows_kernel<RP>, (const float*)rows, R, xqkv, C, v_off, state, slot_stride, y, \
+        tq_launch(grid, 128, smem, stream, 1, few_blocks ? false : true)(delta_scan_rows_kernel<RP>, (const float*)rows, R, xqkv, C, v_off, state, slot_stride, y, \
             heads, kv_heads, dk, dv, tc, vec, cu_seqlens, slots);                                                      \
     } while (0)
     if (rpl == 8) DELTA_ROWS_LAUNCH(8); else if (rpl == 16) DELTA_ROWS_LAUNCH(16); else DELTA_ROWS_LAUNCH(32);
