@@ -592,17 +592,17 @@ def sisepel_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, wa
 
 
 def tasadra_config(width, heads, kv_heads, dim, d_dim, cell, ff, vocab, ranks=(64, 64)):
-    """Six layers: attention, delta rule, differential attention in cells, attention, differential attention reading
-    the first one's rows, delta rule; a dense feed-forward on every layer."""
+    """Six layers: delta rule, attention, differential attention in cells, differential attention reading that one's
+    rows, attention, delta rule; a dense feed-forward on every layer."""
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
            "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
     rule = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": ranks[0], "gate_rank": ranks[1]}
-    dif = lambda src: dict({"heads": heads, "kv_heads": kv_heads, "dim": d_dim, "vdim": dim, "scale": d_dim ** -0.5, "diff": 0.3,
+    dif = lambda src: dict({"heads": heads, "kv_heads": kv_heads, "dim": d_dim, "vdim": dim, "scale": d_dim ** -0.5, "diff": 0.2,
                             "mask": {"size": cell}}, **({} if src is None else {"kv_from": src}))
     mlp = {"kind": "dense", "ff": ff}
-    kinds = [("attention", att), ("channel_delta", rule), ("attention_2", dif(None)), ("attention", att),
-             ("attention_2", dif(2)), ("channel_delta", rule)]
-    return {"architecture": "Tasadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+    kinds = [("channel_delta", rule), ("attention", att), ("attention_2", dif(None)), ("attention_2", dif(2)),
+             ("attention", att), ("channel_delta", rule)]
+    return {"architecture": "Tasadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
             "layers": [{"type": k, "mixer": m, "mlp": mlp} for k, m in kinds]}
 
 
