@@ -152,12 +152,20 @@ VARIANTS = {
                     layer("attention", attention(heads=16, kv_heads=1, dim=128, vdim=64, scale=0.1, rot=rotation(64, 1e4)))],
     # keys of 256 elements in the recurrence, values that no block of sixteen columns divides
     "wide_state": [layer("channel_delta", delta(heads=2, kv_heads=1, dim=256, vdim=21, conv=5), ff=16)],
+    # odd sizes everywhere: width, heads, keys, feed-forward
+    "odd_width": [layer("attention", attention(heads=3, kv_heads=1, dim=10, vdim=6, rot=rotation(6, 77.0, (3.0, 20, 5.0, 1.5))), ff=11),
+                  layer("channel_delta", delta(heads=3, kv_heads=1, dim=5, vdim=9, conv=6), ff=13),
+                  layer("attention_2", differential(heads=5, kv_heads=5, dim=3, vdim=7, size=33), ff=7),
+                  layer("attention_2", differential(heads=5, kv_heads=5, dim=3, vdim=7, size=33, kv_from=2, diff=0.6, scale=1.1))],
 }
+
+
+WIDTHS = {"odd_width": 37}       # a stream no 16-byte access divides
 
 
 @pytest.mark.parametrize("variant", sorted(VARIANTS))
 def test_other_sizes_and_options(tmp_path, variant):
-    cfg = config(VARIANTS[variant], vocab=50, width=36, mult=1.3)
+    cfg = config(VARIANTS[variant], vocab=50, width=WIDTHS.get(variant, 36), mult=1.3)
     folder = write_folder(str(tmp_path / variant), cfg, make_weights(cfg, 5, sharp=2.0, decay_rank=1, gate_rank=3))
     toks = tokens_for(cfg, 200, 31)
     for dtype in ("float32", "bfloat16"):
